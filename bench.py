@@ -1,0 +1,307 @@
+#!/usr/bin/env python
+"""Benchmark of the token-sampling hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the sampler over one batch: configuration 3 of the baseline (256
+rows x V=128256 bf16 Zipf-shaped logits, temperature 0.7, top-p 0.95, per-row xorshift seed
+= row id) per GPU. With N > 1 (one process per GPU under torchrun) every rank samples its own
+256 rows and the int64 ids are all-gathered (weak scaling). Prints ONE JSON line on rank 0.
+
+  value      rows/s with the logits resident in HBM (device-timed, max over ranks)
+  e2e        rows/s through the host-buffer entry of the C ABI: pinned host logits copied to
+             the device, sampled, ids copied back, inside the timed region
+  roofline   logits bytes read per launch / mean kernel time, against the measured HBM copy
+             bandwidth of this pool (MEASURED_PEAKS.json) or the stated fallback
+  cpu_baseline  the reference's own CPU sampler (compiled unmodified in oracle/_ref; the C
+             restatement if that is absent) on this machine's host cores, N = 1 only
+
+--impl reference times the reference's CPU sampler alone on the same batch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sampled_rows_per_s_topp_v128256_bf16"
+WORKLOAD = "c3"
+NBUF = 4  # rotating input buffers: 4 x 65.7 MB > 126 MB of L2
+FALLBACK_HBM_GBS = 6650.0
+
+# DRAM bytes (read + write) of ONE launch of the sampling kernel on the benchmark batch, from
+# the ncu capture summarised in profiles/; None until a capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_pass(x_host, cfg, seeds, threads):
+    """One pass of the reference's CPU sampler over the batch. Returns (wall_s, kind, how)."""
+    import oracle
+    timing = {}
+    if oracle.Reference.available(stable=False):
+        ref = oracle.Reference(stable=False)
+        ref.sample_rows(x_host, cfg.temperature, cfg.topp, seeds, dtype=cfg.dtype, threads=threads,
+                        native=True, timing=timing)
+        return timing["wall_seconds"], "reference", "Sampler::sample<BFloat16> of the unmodified sampler.cpp"
+    r = oracle.Restatement()
+    r.sample_rows(x_host, cfg.temperature, cfg.topp, seeds, dtype=cfg.dtype, threads=threads, timing=timing)
+    return timing["wall_seconds"], "port", "C restatement (float on upcast logits)"
+
+
+def cpu_baseline(x_host, cfg, seeds, budget_cpu_s=15.0):
+    threads = os.cpu_count() or 1
+    rows = x_host.shape[0]
+    wall, kind, how = cpu_reference_pass(x_host, cfg, seeds, threads)  # also warms the pages
+    reps = int(max(1, min(200, budget_cpu_s / max(wall * threads, 1e-6))))
+    t = 0.0
+    for _ in range(reps):
+        w, kind, how = cpu_reference_pass(x_host, cfg, seeds, threads)
+        t += w
+    return {"value": rows * reps / t, "unit": "rows/s", "cores": threads, "kind": kind,
+            "sample": f"{reps} passes over the {rows}-row batch, one fresh Sampler per row, "
+                      f"rows striped over {threads} threads; {how}"}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's own CPU implementation on this box's host cores."""
+    if rank != 0:
+        return
+    import numpy as np
+    from executorch_b200 import workloads as W
+    cfg = W.CONFIGS[WORKLOAD]
+    rows = cfg.rows
+    # same distribution as the device-born benchmark rows; a 64-row host sample tiled to the
+    # batch keeps generation short (the sampler's cost does not depend on which rows repeat)
+    base = W.rows_numpy(WORKLOAD, list(range(64)))
+    x = np.ascontiguousarray(np.tile(base, (rows // 64, 1)))
+    seeds = np.arange(rows, dtype=np.uint64)
+    threads = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_reference_pass(x, cfg, seeds, threads)
+    t, kind, how = 0.0, "", ""
+    for _ in range(args.steps):
+        w, kind, how = cpu_reference_pass(x, cfg, seeds, threads)
+        t += w
+    value = rows * args.steps / t
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "c3: 256 rows x V=128256 bf16 Zipf logits, T=0.7, top-p 0.95, seed=row",
+                   "rows": rows, "vocab": cfg.vocab},
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": kind,
+                         "sample": f"each step = one pass over the {rows}-row batch on {threads} threads; {how}"},
+        "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from executorch_b200 import Sampler, seeds_to_states
+    from executorch_b200 import workloads as W
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sampler has no CPU path")
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = W.CONFIGS[WORKLOAD]
+    rows, vocab = cfg.rows, cfg.vocab
+    total_rows = rows * world
+    warmup = max(args.warmup, 3)
+
+    # inputs born in HBM: NBUF distinct batches for this rank (rows are a function of their id)
+    bufs = [W.rows_torch(WORKLOAD, (rank * NBUF + b) * rows, rows, dev) for b in range(NBUF)]
+    seeds = np.arange(rank * rows, (rank + 1) * rows, dtype=np.uint64)
+    states0 = seeds_to_states(seeds, dev)
+    states = states0.clone()
+    local_ids = torch.empty(rows, dtype=torch.int64, device=dev)
+    all_ids = torch.empty(total_rows, dtype=torch.int64, device=dev) if world > 1 else local_ids
+    sampler = Sampler(vocab, cfg.temperature, cfg.topp, 0, device=dev)
+
+    def step(i):
+        sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
+        if world > 1:
+            dist.all_gather_into_tensor(all_ids, local_ids)
+
+    for i in range(warmup):
+        states.copy_(states0)
+        step(i)
+    torch.cuda.synchronize()
+
+    # ---- device-timed region: K steps, inputs resident
+    k_start = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    k_end = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = sampler.launch_count
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0.record()
+    for i in range(args.steps):
+        k_start[i].record()
+        sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
+        k_end[i].record()
+        if world > 1:
+            dist.all_gather_into_tensor(all_ids, local_ids)
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clock_info = clocks.stop() if rank == 0 else None
+    launches = sampler.launch_count - launches0
+    elapsed_ms = t0.elapsed_time(t1)
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(k_start, k_end))
+    if world > 1:
+        tt = torch.tensor([elapsed_ms, kernel_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms, kernel_ms = float(tt[0]), float(tt[1])
+    value = total_rows * args.steps / (elapsed_ms * 1e-3)
+
+    # ---- end to end through the host-buffer entry of the C ABI (pinned host logits)
+    host_bufs = [b.cpu().view(torch.int16).pin_memory().view(torch.bfloat16) for b in bufs[:2]]
+    host_states = seeds.copy()
+    for i in range(2):
+        host_states[:] = seeds
+        sampler.sample_rows_host(host_bufs[i % 2], host_states)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0 = time.perf_counter()
+    for i in range(args.e2e_steps):
+        ids_host = sampler.sample_rows_host(host_bufs[i % 2], host_states)
+    e_ms = (time.perf_counter() - e0) * 1e3
+    if world > 1:
+        tt = torch.tensor([e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e_ms = float(tt[0])
+    e2e_value = total_rows * args.e2e_steps / (e_ms * 1e-3)
+    h2d = rows * vocab * 2 + rows * 8
+    d2h = rows * 8 + rows * 8
+    assert ids_host.shape == (rows,)
+
+    if rank == 0:
+        peak, which = hbm_peak()
+        algo_bytes = rows * (vocab * 2 + 8 + 16)  # logits once + id + rng state in/out
+        achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": "c3: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0.7, top-p 0.95, seed=row",
+                "rows_per_gpu": rows, "vocab": vocab, "global_rows": total_rows,
+                "l2": f"{NBUF} rotating input batches ({NBUF * rows * vocab * 2 / 1e6:.0f} MB > 126 MB L2)",
+                "exchange": "all_gather of int64 ids (NCCL)" if world > 1 else "none",
+            },
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "peak_source": f"of {which}", "kernel_ms": kernel_ms,
+                         "algorithmic_bytes_per_launch": algo_bytes},
+            "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / args.e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clock_info,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            x_host = host_bufs[0].view(torch.int16).numpy().view(np.uint16)
+            line["cpu_baseline"] = cpu_baseline(x_host, cfg, seeds)
+        print(json.dumps(line), flush=True)
+    sampler.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,389 @@
+// extern "C" surface of the B200 token sampler (declared in include/etb200_sampler.h).
+// Mirrors the conventions of the reference's CUDA shims
+// (backends/cuda/runtime/shims/rand.cu:175-237): argument checks return InvalidArgument,
+// unsupported dtypes NotSupported, CUDA failures Internal; nothing throws.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <ctime>
+#include <new>
+
+#include "../../include/etb200_sampler.h"
+#include "sampler_kernels.cuh"
+
+using namespace etb200;
+
+struct etb200_sampler {
+  int device = 0;
+  int vocab = 0;
+  float inv_temperature = 0.0f;  // reciprocal of temperature, 0 for greedy (sampler.h:78)
+  float topp = 0.9f;
+  int topk = 0;
+  unsigned long long* d_state = nullptr;  // the handle's own xorshift64* state
+  int64_t* d_token = nullptr;             // output slot of the single-row call
+  int* d_status = nullptr;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int sm_count = 0;
+  // staging for the host-buffer entry point
+  void* d_stage = nullptr;
+  size_t stage_bytes = 0;
+  unsigned long long* d_stage_states = nullptr;
+  int64_t* d_stage_ids = nullptr;
+  int64_t stage_rows = 0;
+  uint64_t launches = 0;
+  ExpTable table;
+};
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+etb200_error_t fail(etb200_error_t code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define ETB_CHECK_ARG(cond, ...) \
+  do {                           \
+    if (!(cond)) return fail(ETB200_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+#define ETB_CUDA(expr)                                                              \
+  do {                                                                              \
+    cudaError_t e_ = (expr);                                                        \
+    if (e_ != cudaSuccess)                                                          \
+      return fail(ETB200_INTERNAL, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+// Makes the handle's device current for the duration of a call.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int dev) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != dev) {
+      err = cudaSetDevice(dev);
+      switched = (err == cudaSuccess);
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case kDtypeFloat:
+      return 4;
+    case kDtypeHalf:
+    case kDtypeBFloat16:
+    case kDtypeUInt16:
+      return 2;
+    default:
+      return 0;
+  }
+}
+
+float inv_temperature_of(float temperature) {
+  // static_cast<bool>(temperature) ? 1.0f / temperature : 0  (sampler.cpp:179)
+  return (temperature != 0.0f) ? 1.0f / temperature : 0.0f;
+}
+
+etb200_error_t create_impl(
+    int32_t vocab, float temperature, float topp, uint64_t seed, int32_t device,
+    etb200_sampler_t** out) {
+  ETB_CHECK_ARG(out != nullptr, "out_handle is null");
+  *out = nullptr;
+  ETB_CHECK_ARG(vocab >= 1, "vocab_size must be >= 1, got %d", vocab);
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0) {
+    return fail(ETB200_INTERNAL, "no CUDA device available (%s); this library has no CPU path",
+                e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  }
+  ETB_CHECK_ARG(device >= 0 && device < ndev, "device %d out of range [0, %d)", device, ndev);
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess)
+    return fail(ETB200_INTERNAL, "cudaSetDevice(%d) failed: %s", device, cudaGetErrorString(guard.err));
+  etb200_sampler* h = new (std::nothrow) etb200_sampler();
+  if (!h) return fail(ETB200_MEMORY_ALLOCATION_FAILED, "out of host memory");
+  h->device = device;
+  h->vocab = vocab;
+  h->inv_temperature = inv_temperature_of(temperature);
+  h->topp = topp;
+  make_exp_table(&h->table);
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) {
+    delete h;
+    return fail(ETB200_INTERNAL, "cudaGetDeviceProperties failed: %s", cudaGetErrorString(e));
+  }
+  if (prop.major < 10) {
+    delete h;
+    return fail(ETB200_NOT_SUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                device, prop.major, prop.minor);
+  }
+  h->sm_count = prop.multiProcessorCount;
+  e = cudaMalloc(&h->d_state, sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMalloc(&h->d_token, sizeof(int64_t));
+  if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(int));
+  unsigned long long s = seed;
+  if (e == cudaSuccess) e = cudaMemcpy(h->d_state, &s, sizeof(s), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(h->d_state);
+    cudaFree(h->d_token);
+    cudaFree(h->d_status);
+    delete h;
+    return fail(ETB200_MEMORY_ALLOCATION_FAILED, "device allocation failed: %s", cudaGetErrorString(e));
+  }
+  *out = h;
+  return ETB200_OK;
+}
+
+int grid_blocks(const etb200_sampler* h, int dtype, int64_t rows) {
+  const int64_t resident = (int64_t)h->sm_count * sample_kernel_max_blocks_per_sm(dtype);
+  return (int)(rows < resident ? rows : resident);
+}
+
+etb200_error_t ensure_scratch(etb200_sampler* h, int blocks) {
+  const size_t need = sampler_scratch_bytes(h->vocab, blocks);
+  if (need <= h->scratch_bytes) return ETB200_OK;
+  if (h->scratch) {
+    ETB_CUDA(cudaDeviceSynchronize());
+    ETB_CUDA(cudaFree(h->scratch));
+    h->scratch = nullptr;
+    h->scratch_bytes = 0;
+  }
+  cudaError_t e = cudaMalloc(&h->scratch, need);
+  if (e != cudaSuccess)
+    return fail(ETB200_MEMORY_ALLOCATION_FAILED, "cudaMalloc of %zu scratch bytes failed: %s", need,
+                cudaGetErrorString(e));
+  h->scratch_bytes = need;
+  return ETB200_OK;
+}
+
+// Shared by the device- and host-buffer entry points. All pointers are device pointers.
+etb200_error_t sample_rows_device(
+    etb200_sampler* h, const void* logits, int dtype, int64_t rows, int64_t row_stride,
+    unsigned long long* rng_states, int64_t* out_ids, cudaStream_t stream) {
+  if (rows == 0) return ETB200_OK;
+  if (h->inv_temperature == 0.0f) {
+    // greedy: no coin is drawn and the RNG state does not move (sampler.cpp:226-228)
+    const int blocks = (int)(rows < (int64_t)h->sm_count * 4 ? rows : (int64_t)h->sm_count * 4);
+    ETB_CUDA(launch_argmax_rows(dtype, logits, rows, h->vocab, row_stride, out_ids, blocks, stream));
+    h->launches += 1;
+    return ETB200_OK;
+  }
+  if (dtype == kDtypeUInt16) {
+    return fail(ETB200_NOT_SUPPORTED,
+                "UInt16 logits are raw integers: only temperature 0 (argmax) is meaningful for them");
+  }
+  if (h->topk > 0 && h->topk < h->vocab) {
+    return fail(ETB200_NOT_SUPPORTED, "top-k sampling (set_topk(%d)) is not built yet", h->topk);
+  }
+  if (rng_states == nullptr) {
+    ETB_CHECK_ARG(rows == 1, "rng_states may be NULL only for a single row (rows = %lld)", (long long)rows);
+    rng_states = h->d_state;
+  }
+  const bool use_topp = !(h->topp <= 0.0f || h->topp >= 1.0f);
+  const int blocks = grid_blocks(h, dtype, rows);
+  if (use_topp) {
+    etb200_error_t err = ensure_scratch(h, blocks);
+    if (err != ETB200_OK) return err;
+  }
+  ETB_CUDA(launch_sample_rows(
+      dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, rng_states, out_ids,
+      h->scratch, blocks, h->table, h->d_status, stream));
+  h->launches += 1;
+  return ETB200_OK;
+}
+
+etb200_error_t check_common(
+    etb200_sampler* h, const void* logits, int dtype, int64_t rows, int64_t row_stride,
+    const void* out_ids) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  ETB_CHECK_ARG(rows >= 0, "rows must be >= 0, got %lld", (long long)rows);
+  if (rows == 0) return ETB200_OK;
+  ETB_CHECK_ARG(logits != nullptr, "logits is null");
+  ETB_CHECK_ARG(out_ids != nullptr, "output pointer is null");
+  if (dtype_size(dtype) == 0) {
+    // sample_from_logits aborts on other dtypes (util.h:30-34); here it is an error code
+    return fail(ETB200_NOT_SUPPORTED, "unsupported logits dtype code %d (Half 5, Float 6, BFloat16 15, UInt16 27)", dtype);
+  }
+  ETB_CHECK_ARG(rows == 1 || row_stride == 0 || row_stride >= h->vocab,
+                "row_stride_elems (%lld) is smaller than vocab_size (%d) and not 0", (long long)row_stride, h->vocab);
+  return ETB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+etb200_error_t etb200_sampler_create(
+    int32_t vocab_size, float temperature, float topp, uint64_t rng_seed, int32_t device,
+    etb200_sampler_t** out_handle) {
+  return create_impl(vocab_size, temperature, topp, rng_seed, device, out_handle);
+}
+
+etb200_error_t etb200_sampler_create_default(
+    int32_t vocab_size, float temperature, int32_t device, etb200_sampler_t** out_handle) {
+  return create_impl(vocab_size, temperature, 0.9f, (uint64_t)std::time(nullptr), device, out_handle);
+}
+
+etb200_error_t etb200_sampler_destroy(etb200_sampler_t* h) {
+  if (!h) return ETB200_OK;
+  DeviceGuard guard(h->device);
+  cudaDeviceSynchronize();
+  cudaFree(h->d_state);
+  cudaFree(h->d_token);
+  cudaFree(h->d_status);
+  cudaFree(h->scratch);
+  cudaFree(h->d_stage);
+  cudaFree(h->d_stage_states);
+  cudaFree(h->d_stage_ids);
+  delete h;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_set_temperature(etb200_sampler_t* h, float temperature) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  if (temperature < 0.0f) temperature = 0.0f;
+  h->inv_temperature = inv_temperature_of(temperature);
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_set_topk(etb200_sampler_t* h, int32_t topk) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  h->topk = topk;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_get_rng_state(etb200_sampler_t* h, uint64_t* out_state) {
+  ETB_CHECK_ARG(h != nullptr && out_state != nullptr, "null argument");
+  DeviceGuard guard(h->device);
+  unsigned long long s = 0;
+  ETB_CUDA(cudaMemcpy(&s, h->d_state, sizeof(s), cudaMemcpyDeviceToHost));
+  *out_state = s;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_set_rng_state(etb200_sampler_t* h, uint64_t state) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  DeviceGuard guard(h->device);
+  unsigned long long s = state;
+  ETB_CUDA(cudaMemcpy(h->d_state, &s, sizeof(s), cudaMemcpyHostToDevice));
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_sample(
+    etb200_sampler_t* h, const void* logits_device, int32_t dtype, void* stream,
+    int32_t* out_token) {
+  etb200_error_t err = check_common(h, logits_device, dtype, 1, 0, out_token);
+  if (err != ETB200_OK) return err;
+  DeviceGuard guard(h->device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  err = sample_rows_device(h, logits_device, dtype, 1, h->vocab, nullptr, h->d_token, st);
+  if (err != ETB200_OK) return err;
+  int64_t tok = 0;
+  ETB_CUDA(cudaMemcpyAsync(&tok, h->d_token, sizeof(tok), cudaMemcpyDeviceToHost, st));
+  ETB_CUDA(cudaStreamSynchronize(st));
+  *out_token = (int32_t)tok;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_sample_rows(
+    etb200_sampler_t* h, const void* logits_device, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* out_ids_device, void* stream) {
+  etb200_error_t err = check_common(h, logits_device, dtype, rows, row_stride_elems, out_ids_device);
+  if (err != ETB200_OK) return err;
+  DeviceGuard guard(h->device);
+  return sample_rows_device(
+      h, logits_device, dtype, rows, row_stride_elems,
+      reinterpret_cast<unsigned long long*>(rng_states_device), out_ids_device,
+      static_cast<cudaStream_t>(stream));
+}
+
+etb200_error_t etb200_sampler_sample_rows_host(
+    etb200_sampler_t* h, const void* logits_host, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_host, int64_t* out_ids_host, void* stream) {
+  etb200_error_t err = check_common(h, logits_host, dtype, rows, row_stride_elems, out_ids_host);
+  if (err != ETB200_OK) return err;
+  if (rows == 0) return ETB200_OK;
+  const bool greedy = (h->inv_temperature == 0.0f);
+  ETB_CHECK_ARG(greedy || rng_states_host != nullptr, "rng_states_host is null");
+  DeviceGuard guard(h->device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t esz = dtype_size(dtype);
+  const size_t bytes = ((size_t)(rows - 1) * (size_t)row_stride_elems + (size_t)h->vocab) * esz;
+  if (bytes > h->stage_bytes) {
+    ETB_CUDA(cudaDeviceSynchronize());
+    cudaFree(h->d_stage);
+    h->d_stage = nullptr;
+    h->stage_bytes = 0;
+    cudaError_t e = cudaMalloc(&h->d_stage, bytes);
+    if (e != cudaSuccess)
+      return fail(ETB200_MEMORY_ALLOCATION_FAILED, "cudaMalloc of %zu staging bytes failed: %s", bytes,
+                  cudaGetErrorString(e));
+    h->stage_bytes = bytes;
+  }
+  if (rows > h->stage_rows) {
+    ETB_CUDA(cudaDeviceSynchronize());
+    cudaFree(h->d_stage_states);
+    cudaFree(h->d_stage_ids);
+    h->d_stage_states = nullptr;
+    h->d_stage_ids = nullptr;
+    h->stage_rows = 0;
+    cudaError_t e = cudaMalloc(&h->d_stage_states, sizeof(unsigned long long) * (size_t)rows);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_stage_ids, sizeof(int64_t) * (size_t)rows);
+    if (e != cudaSuccess)
+      return fail(ETB200_MEMORY_ALLOCATION_FAILED, "cudaMalloc of staging ids/states failed: %s",
+                  cudaGetErrorString(e));
+    h->stage_rows = rows;
+  }
+  ETB_CUDA(cudaMemcpyAsync(h->d_stage, logits_host, bytes, cudaMemcpyHostToDevice, st));
+  if (!greedy) {
+    ETB_CUDA(cudaMemcpyAsync(h->d_stage_states, rng_states_host, sizeof(uint64_t) * (size_t)rows,
+                             cudaMemcpyHostToDevice, st));
+  }
+  err = sample_rows_device(h, h->d_stage, dtype, rows, row_stride_elems, h->d_stage_states,
+                           h->d_stage_ids, st);
+  if (err != ETB200_OK) return err;
+  ETB_CUDA(cudaMemcpyAsync(out_ids_host, h->d_stage_ids, sizeof(int64_t) * (size_t)rows,
+                           cudaMemcpyDeviceToHost, st));
+  if (!greedy) {
+    ETB_CUDA(cudaMemcpyAsync(rng_states_host, h->d_stage_states, sizeof(uint64_t) * (size_t)rows,
+                             cudaMemcpyDeviceToHost, st));
+  }
+  ETB_CUDA(cudaStreamSynchronize(st));
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_launch_count(etb200_sampler_t* h, uint64_t* out_count) {
+  ETB_CHECK_ARG(h != nullptr && out_count != nullptr, "null argument");
+  *out_count = h->launches;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_selftest_expf(
+    const float* x_device, float* y_device, int64_t n, void* stream) {
+  ETB_CHECK_ARG(n >= 0, "n must be >= 0");
+  if (n == 0) return ETB200_OK;
+  ETB_CHECK_ARG(x_device != nullptr && y_device != nullptr, "null argument");
+  ExpTable table;
+  make_exp_table(&table);
+  ETB_CUDA(launch_expf_selftest(x_device, y_device, n, table, static_cast<cudaStream_t>(stream)));
+  return ETB200_OK;
+}
+
+const char* etb200_last_error_message(void) { return g_err; }
+
+uint32_t etb200_sampler_abi_version(void) { return 1; }
+
+}  // extern "C"

@@ -1,0 +1,783 @@
+// Token-sampling kernels for sm_100a: greedy argmax, multinomial and top-p (nucleus)
+// sampling of rows x vocab logits, reproducing ExecuTorch's CPU sampler
+// (extension/llm/sampler/sampler.cpp) bit for bit on the fp32 upcast of the logits.
+//
+// Work decomposition: one thread block per row (blocks stride over the rows of a batch).
+// Logits are read in place (bf16 / fp16 / fp32, 128-bit loads when the row is 16-byte
+// aligned) and never written. A sampled row makes these passes:
+//
+//   1. max of the temperature-scaled logits                      (HBM read of the row)
+//   2. e_i = expf(x_i - max), exact sequential-order float sum S (row re-read, L2 resident);
+//      top-p also appends (e_i, i) of every possible nucleus member to a per-block list
+//   3a. multinomial: exact running cdf of e_i / S in index order until it exceeds the coin
+//   3b. top-p: pick a value threshold from a histogram of the list, compact the survivors
+//       with p_i = e_i / S >= cutoff, LSD-radix sort them (probability descending, stable =
+//       index ascending), replay the reference's cumulative sums exactly, draw.
+//
+// The candidate lists of 3b live in global scratch memory owned by the caller of the launch
+// functions (two buffers of vocab entries per resident block).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "exact_math.cuh"
+#include "sampler_kernels.cuh"
+
+namespace etb200 {
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kChunk = 8;                   // consecutive logits per thread per tile
+constexpr int kTile = kThreads * kChunk;    // logits per tile
+constexpr int kHistShift = 19;              // histogram bin = float bits >> 19 (exponent + 4 mantissa bits)
+constexpr int kHistBins = (0x3F800000 >> kHistShift) + 2;  // values in (0, 1]
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+
+struct Entry {
+  uint32_t key;  // float bits of e_i (list A) or p_i (sorted lists); positive floats order like integers
+  int32_t idx;   // token index
+};
+
+struct __align__(16) Shared {
+  uint64_t exp_tab[kExpTableSize];
+  SeqSummary wsum[kWarps];
+  int wcnt[2][kWarps];
+  float redf[kWarps];
+  int redi[kWarps];
+  float s_bcast;
+  int first;
+  int hit_found;
+  int hit_idx;
+  float hit_val;
+  int misc_i[4];
+  float misc_f[4];
+  union {
+    struct {
+      unsigned cnt[kHistBins];
+      float mass[kHistBins];
+    } hist;
+    struct {
+      unsigned digit[kRadix];
+      unsigned offs[kRadix];
+      unsigned short wdig[kWarps][kRadix];
+    } radix;
+  } u;
+};
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Loads kChunk consecutive logits starting at element i0 of a row, upcast exactly to fp32.
+// Elements at or beyond `vocab` are returned as 0 and must be masked by the caller.
+template <typename T>
+__device__ __forceinline__ void load_chunk(
+    const T* __restrict__ row, int i0, int vocab, bool vec_ok, float (&x)[kChunk]) {
+  constexpr int kPerVec = 16 / sizeof(T);
+  if (vec_ok && i0 + kChunk <= vocab) {
+#pragma unroll
+    for (int v = 0; v < kChunk / kPerVec; ++v) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + i0) + v);
+      const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < kPerVec; ++j) x[v * kPerVec + j] = to_f32(p[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) {
+      const int i = i0 + j;
+      x[j] = (i < vocab) ? to_f32(row[i]) : 0.0f;
+    }
+  }
+}
+
+__device__ __forceinline__ float block_max(Shared& sm, float v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sm.redf[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = sm.redf[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) r = fmaxf(r, sm.redf[w]);
+  return r;
+}
+
+// Exclusive block-wide prefix count of a per-thread count; *total gets the block sum.
+__device__ __forceinline__ int block_excl_count(Shared& sm, int cnt, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = cnt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += o;
+  }
+  __syncthreads();
+  if (lane == 31) sm.redi[warp] = inc;
+  __syncthreads();
+  int pre = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const int c = sm.redi[w];
+    if (w < warp) pre += c;
+    tot += c;
+  }
+  *total = tot;
+  return pre + inc - cnt;
+}
+
+// ---------------------------------------------------------------------------------------
+// One tile of the exact sequential float sum. Thread t holds the kChunk consecutive terms
+// v[] that follow the terms of threads 0..t-1. `s` is the running sum in front of the
+// tile on entry and behind it on return (block-uniform).
+//
+// With kSearch, also looks for the first term after which the running sum exceeds `thr`
+// (terms at position >= limit, counted from pos0 of thread 0's first term, are padding
+// zeros and never match); on a match returns true with the position in *hit_pos and the
+// sum reached there in *hit_sum (block-uniform), and `s` is then not meaningful.
+// ---------------------------------------------------------------------------------------
+template <bool kSearch>
+__device__ __forceinline__ bool seqsum_tile(
+    Shared& sm, const float (&v)[kChunk], float& s, float thr, int pos0, int limit,
+    int* hit_pos, float* hit_sum) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int consumed = 0;
+  while (true) {
+    const int kb = seq_kb(s);
+    const int n_s = seq_n(s);
+    SeqSummary mine;
+    seq_identity(&mine);
+    if (tid >= consumed) {
+      if (kb >= 27) {
+        const float inv_u = seq_inv_u(kb);
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) seq_push_scaled(&mine, v[j], inv_u);
+      } else {
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) seq_push(&mine, v[j], kb);
+      }
+    }
+    SeqSummary inc = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      SeqSummary o;
+      o.a0 = __shfl_up_sync(0xffffffffu, inc.a0, d);
+      o.a1 = __shfl_up_sync(0xffffffffu, inc.a1, d);
+      if (lane >= d) inc = seq_compose(o, inc);
+    }
+    SeqSummary excl;
+    excl.a0 = __shfl_up_sync(0xffffffffu, inc.a0, 1);
+    excl.a1 = __shfl_up_sync(0xffffffffu, inc.a1, 1);
+    if (lane == 0) seq_identity(&excl);
+    __syncthreads();  // previous readers of wsum / first / s_bcast are done
+    if (lane == 31) sm.wsum[warp] = inc;
+    if (tid == 0) {
+      sm.first = kThreads;
+      sm.hit_found = 0;
+    }
+    __syncthreads();
+    // every warp redundantly scans the kWarps warp totals with shuffles
+    SeqSummary wt;
+    seq_identity(&wt);
+    if (lane < kWarps) wt = sm.wsum[lane];
+#pragma unroll
+    for (int d = 1; d < kWarps; d <<= 1) {
+      SeqSummary o;
+      o.a0 = __shfl_up_sync(0xffffffffu, wt.a0, d);
+      o.a1 = __shfl_up_sync(0xffffffffu, wt.a1, d);
+      if (lane >= d) wt = seq_compose(o, wt);
+    }
+    SeqSummary pre, total;
+    pre.a0 = __shfl_sync(0xffffffffu, wt.a0, warp > 0 ? warp - 1 : 0);
+    pre.a1 = __shfl_sync(0xffffffffu, wt.a1, warp > 0 ? warp - 1 : 0);
+    if (warp == 0) seq_identity(&pre);
+    total.a0 = __shfl_sync(0xffffffffu, wt.a0, kWarps - 1);
+    total.a1 = __shfl_sync(0xffffffffu, wt.a1, kWarps - 1);
+    pre = seq_compose(pre, excl);
+    const int n_in = seq_apply(n_s, pre);
+    const int n_out = seq_apply(n_in, mine);
+    const bool active = tid >= consumed;
+    bool flag = active && (n_out >= kSeqLimit);
+    if (kSearch) {
+      if (active && n_out < kSeqLimit && seq_value(kb, n_out) > thr) flag = true;
+    }
+    const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+    if (ballot != 0 && lane == 0) atomicMin(&sm.first, warp * 32 + __ffs(ballot) - 1);
+    __syncthreads();
+    const int first = sm.first;
+    if (first == kThreads) {
+      // nothing left the binade: the whole tile is summarised exactly
+      s = seq_value(kb, seq_apply(n_s, total));
+      return false;
+    }
+    if (tid == first) {
+      // The sum in front of this chunk is exact; redo the chunk with real float additions
+      // (it leaves the binade here, or it contains the searched position).
+      float acc = seq_value(kb, n_in);
+      bool found = false;
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) {
+        acc = __fadd_rn(acc, v[j]);
+        if (kSearch) {
+          const int pos = pos0 + tid * kChunk + j;
+          if (!found && acc > thr && pos < limit) {
+            found = true;
+            sm.hit_found = 1;
+            sm.hit_idx = pos;
+            sm.hit_val = acc;
+          }
+        }
+      }
+      sm.s_bcast = acc;
+    }
+    __syncthreads();
+    s = sm.s_bcast;
+    if (kSearch && sm.hit_found) {
+      *hit_pos = sm.hit_idx;
+      *hit_sum = sm.hit_val;
+      return true;
+    }
+    consumed = first + 1;
+    if (consumed >= kThreads) return false;
+  }
+}
+
+// xorshift64* step and 24-bit coin of the reference (sampler.cpp:210-220).
+__device__ __forceinline__ float next_coin(unsigned long long* state) {
+  unsigned long long s = *state;
+  s ^= s >> 12;
+  s ^= s << 25;
+  s ^= s >> 27;
+  *state = s;
+  const unsigned u = (unsigned)((s * 0x2545F4914F6CDD1Dull) >> 32);
+  return (float)(u >> 8) / 16777216.0f;
+}
+
+// Scaled logits of one chunk: x = logit * inv_temperature in fp32 (sampler.cpp:231-233).
+template <typename T>
+__device__ __forceinline__ void scaled_chunk(
+    const T* __restrict__ row, int i0, int vocab, bool vec_ok, float inv_t, float (&x)[kChunk]) {
+  load_chunk<T>(row, i0, vocab, vec_ok, x);
+#pragma unroll
+  for (int j = 0; j < kChunk; ++j) x[j] = __fmul_rn(x[j], inv_t);
+}
+
+// ---------------------------------------------------------------------------------------
+// Stable LSD radix sort pass over a list of n entries, descending in the 8-bit digit at
+// `shift`. One block; src and dst are distinct global buffers.
+// ---------------------------------------------------------------------------------------
+__device__ void radix_pass_desc(Shared& sm, const Entry* src, Entry* dst, int n, int shift) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __syncthreads();
+  for (int d = tid; d < kRadix; d += kThreads) sm.u.radix.digit[d] = 0;
+  __syncthreads();
+  for (int i = tid; i < n; i += kThreads) {
+    atomicAdd(&sm.u.radix.digit[(src[i].key >> shift) & (kRadix - 1)], 1u);
+  }
+  __syncthreads();
+  // offs[d] = number of entries with a larger digit (descending order): suffix sums over
+  // the 256 digits, 8 warps of 32 digits each
+  if (tid < kRadix) {
+    const unsigned c = sm.u.radix.digit[tid];
+    unsigned incl = c;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned o = __shfl_down_sync(0xffffffffu, incl, d);
+      if (lane + d < 32) incl += o;
+    }
+    sm.u.radix.offs[tid] = incl - c;
+    if (lane == 0) sm.redi[warp] = (int)incl;
+  }
+  __syncthreads();
+  if (tid < kRadix) {
+    unsigned above = 0;
+    for (int w = warp + 1; w < kRadix / 32; ++w) above += (unsigned)sm.redi[w];
+    sm.u.radix.offs[tid] += above;
+  }
+  __syncthreads();
+  for (int base = 0; base < n; base += kThreads) {
+    const int i = base + tid;
+    const bool valid = i < n;
+    Entry e;
+    e.key = 0;
+    e.idx = 0;
+    if (valid) e = src[i];
+    const unsigned dg = valid ? ((e.key >> shift) & (kRadix - 1)) : 0xFFFFFFFFu;
+    for (int d = lane; d < kRadix; d += 32) sm.u.radix.wdig[warp][d] = 0;
+    __syncwarp();
+    // rank among the lanes of this warp that hold the same digit, in lane (= list) order
+    const unsigned peers = __match_any_sync(0xffffffffu, dg);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank == 0) sm.u.radix.wdig[warp][dg] = (unsigned short)__popc(peers);
+    __syncthreads();
+    if (tid < kRadix) {
+      // per digit: turn the warps' counts into exclusive offsets; digit[] gets the tile total
+      unsigned run = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const unsigned c = sm.u.radix.wdig[w][tid];
+        sm.u.radix.wdig[w][tid] = (unsigned short)run;
+        run += c;
+      }
+      sm.u.radix.digit[tid] = run;
+    }
+    __syncthreads();
+    if (valid) dst[sm.u.radix.offs[dg] + sm.u.radix.wdig[warp][dg] + rank] = e;
+    __syncthreads();
+    if (tid < kRadix) sm.u.radix.offs[tid] += sm.u.radix.digit[tid];
+  }
+  __syncthreads();
+}
+
+// Exact cumulative sum over the key floats of a sorted list, looking for the first
+// position (below `limit`) where it exceeds thr. Returns true with position and sum, else
+// false with the total in *total.
+__device__ bool list_search(
+    Shared& sm, const Entry* list, int n, int limit, float thr, int* pos, float* sum,
+    float* total) {
+  float s = 0.0f;
+  for (int base = 0; base < n; base += kTile) {
+    float v[kChunk];
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) {
+      const int i = base + threadIdx.x * kChunk + j;
+      v[j] = (i < n && i < limit) ? bits_f32(list[i].key) : 0.0f;
+    }
+    if (seqsum_tile<true>(sm, v, s, thr, base, limit, pos, sum)) return true;
+    if (base + kTile >= limit) break;  // nothing searchable beyond the limit
+  }
+  *total = s;
+  return false;
+}
+
+// ---------------------------------------------------------------------------------------
+// The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
+// otherwise. Follows Sampler::sample<float> (sampler.cpp:222-251).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
+    const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
+    float topp, unsigned long long* __restrict__ rng_states, int64_t* __restrict__ out_ids,
+    Entry* scratch, ExpTable table, int* __restrict__ status) {
+  (void)status;
+  __shared__ Shared sm;
+  const int tid = threadIdx.x;
+  if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
+  __syncthreads();
+  const bool use_topp = !(topp <= 0.0f || topp >= 1.0f);
+  Entry* listA = scratch + (size_t)blockIdx.x * 2 * (size_t)vocab;
+  Entry* listB = listA + vocab;
+
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* row = logits + r * row_stride;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+
+    // ---- pass 1: max of the scaled logits (softmax, sampler.cpp:191-196)
+    float mx = -INFINITY;
+    for (int base = 0; base < vocab; base += kTile) {
+      const int i0 = base + tid * kChunk;
+      float x[kChunk];
+      scaled_chunk<T>(row, i0, vocab, vec_ok, inv_t, x);
+      if (i0 + kChunk <= vocab) {
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) mx = fmaxf(mx, x[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j)
+          if (i0 + j < vocab) mx = fmaxf(mx, x[j]);
+      }
+    }
+    mx = block_max(sm, mx);
+
+    // the coin is drawn once per sampled row (sampler.cpp:237)
+    if (tid == 0) {
+      unsigned long long st = rng_states[r];
+      sm.misc_f[0] = next_coin(&st);
+      rng_states[r] = st;
+    }
+
+    // ---- pass 2: e_i = expf(x_i - max) and their float sum in index order
+    // (sampler.cpp:198-203). Top-p also lists every entry that can pass the cutoff crop of
+    // sampler.cpp:136-143: p_i >= cutoff needs e_i >= cutoff * S and S >= 1 (the maximum
+    // contributes exactly 1), so e_i >= cutoff * (1 - 2^-20) is necessary.
+    const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
+    const float e_floor = use_topp ? cutoff * 0.999999f : 0.0f;
+    float s = 0.0f;
+    int n_a = 0;
+    for (int base = 0; base < vocab; base += kTile) {
+      const int i0 = base + tid * kChunk;
+      float x[kChunk], e[kChunk];
+      scaled_chunk<T>(row, i0, vocab, vec_ok, inv_t, x);
+      int cnt = 0;
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) {
+        e[j] = (i0 + j < vocab) ? expf_ref(__fsub_rn(x[j], mx), sm.exp_tab) : 0.0f;
+        if (use_topp && (i0 + j < vocab) && e[j] >= e_floor) ++cnt;
+      }
+      if (use_topp) {
+        int tot;
+        int off = n_a + block_excl_count(sm, cnt, &tot);
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) {
+          if ((i0 + j < vocab) && e[j] >= e_floor) {
+            Entry en;
+            en.key = f32_bits(e[j]);
+            en.idx = i0 + j;
+            listA[off++] = en;
+          }
+        }
+        n_a += tot;
+      }
+      int hp;
+      float hs;
+      seqsum_tile<false>(sm, e, s, 0.0f, base, vocab, &hp, &hs);
+    }
+    const float sum = s;
+    __syncthreads();
+    const float coin = sm.misc_f[0];
+    int token;
+
+    if (!use_topp) {
+      // ---- pass 3a: sample_mult (sampler.cpp:58-70): running float cdf of p_i = e_i / S
+      token = vocab - 1;
+      float cdf = 0.0f;
+      for (int base = 0; base < vocab; base += kTile) {
+        const int i0 = base + tid * kChunk;
+        float x[kChunk], p[kChunk];
+        scaled_chunk<T>(row, i0, vocab, vec_ok, inv_t, x);
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) {
+          const float e = (i0 + j < vocab) ? expf_ref(__fsub_rn(x[j], mx), sm.exp_tab) : 0.0f;
+          p[j] = __fdiv_rn(e, sum);
+        }
+        int hp;
+        float hs;
+        if (seqsum_tile<true>(sm, p, cdf, coin, base, vocab, &hp, &hs)) {
+          token = hp;
+          break;
+        }
+      }
+    } else {
+      // ---- pass 3b: sample_topp (sampler.cpp:122-171)
+      __threadfence_block();
+      __syncthreads();
+      // histogram of the listed e values: counts and approximate mass per bin
+      for (int b = tid; b < kHistBins; b += kThreads) {
+        sm.u.hist.cnt[b] = 0;
+        sm.u.hist.mass[b] = 0.0f;
+      }
+      __syncthreads();
+      for (int i = tid; i < n_a; i += kThreads) {
+        const uint32_t k = listA[i].key;
+        int b = (int)(k >> kHistShift);
+        b = b < kHistBins ? b : kHistBins - 1;
+        atomicAdd(&sm.u.hist.cnt[b], 1u);
+        atomicAdd(&sm.u.hist.mass[b], bits_f32(k));
+      }
+      __syncthreads();
+      // Lowest bin to keep: the largest b whose bins >= b hold clearly more than topp of the
+      // mass. The margin covers the rounding of the approximate masses and of the reference's
+      // own running sum; the choice only has to be safe, not tight, and is verified below.
+      if (tid < 32) {
+        float acc = 0.0f;
+        unsigned cacc = 0;
+        int chosen = 0, chosen_cnt = 0;
+        bool done = false;
+        for (int hi = kHistBins - 1; hi >= 0 && !done; hi -= 32) {
+          const int b = hi - tid;
+          float m = (b >= 0) ? sm.u.hist.mass[b] : 0.0f;
+          unsigned c = (b >= 0) ? sm.u.hist.cnt[b] : 0u;
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const float om = __shfl_up_sync(0xffffffffu, m, d);
+            const unsigned oc = __shfl_up_sync(0xffffffffu, c, d);
+            if (tid >= d) {
+              m += om;
+              c += oc;
+            }
+          }
+          const float mass_above = acc + m;
+          const float cnt_above = (float)(cacc + c);
+          const float need = sum * (topp * 1.002f + 0.001f + cnt_above * 4.8e-7f);
+          const unsigned ok = __ballot_sync(0xffffffffu, b >= 0 && mass_above >= need);
+          if (ok) {
+            const int sel = __ffs(ok) - 1;
+            chosen = hi - sel;
+            chosen_cnt = (int)(cacc + __shfl_sync(0xffffffffu, c, sel));
+            done = true;
+          }
+          acc += __shfl_sync(0xffffffffu, m, 31);
+          cacc += __shfl_sync(0xffffffffu, c, 31);
+        }
+        if (tid == 0) {
+          // The sort below ping-pongs into the free space behind list A, which must hold the
+          // survivors; if it cannot, take the complete candidate set (then list A may be
+          // overwritten because no second attempt is ever needed).
+          if (!done || n_a + chosen_cnt > vocab) chosen = 0;
+          sm.misc_i[1] = chosen;
+        }
+      }
+      __syncthreads();
+      int bin_lo = sm.misc_i[1];
+      int n_b = 0;
+      bool have = false;
+      int last_idx = 0;
+      float cum = 0.0f;
+      for (int attempt = 0; attempt < 2 && !have; ++attempt) {
+        // compact list A -> list B: survivors of the value threshold that pass the cutoff
+        // crop, with their probabilities, still in index order
+        n_b = 0;
+        const uint32_t key_lo = (uint32_t)bin_lo << kHistShift;
+        for (int base = 0; base < n_a; base += kThreads) {
+          const int i = base + tid;
+          Entry en;
+          en.key = 0;
+          en.idx = 0;
+          bool keep = false;
+          if (i < n_a) {
+            en = listA[i];
+            if (en.key >= key_lo) {
+              const float p = __fdiv_rn(bits_f32(en.key), sum);
+              keep = p >= cutoff;
+              en.key = f32_bits(p);
+            }
+          }
+          int tot;
+          const int off = n_b + block_excl_count(sm, keep ? 1 : 0, &tot);
+          if (keep) listB[off] = en;
+          n_b += tot;
+        }
+        __threadfence_block();
+        __syncthreads();
+        // sort by probability, descending; equal probabilities keep index order.
+        // Passes ping-pong B -> A2 -> B ...; list A must survive for a second attempt, so
+        // the partner buffer is the tail of list A's allocation only when it is free.
+        Entry* ping = listB;
+        Entry* pong = (n_a + n_b <= vocab) ? listA + n_a : listA;
+        for (int pass = 0; pass < 32 / kRadixBits; ++pass) {
+          radix_pass_desc(sm, ping, pong, n_b, pass * kRadixBits);
+          __threadfence_block();
+          Entry* t = ping;
+          ping = pong;
+          pong = t;
+        }
+        __syncthreads();
+        // after an even number of passes the sorted list is back in listB (== ping)
+        int pos;
+        float hs, total;
+        if (list_search(sm, ping, n_b, n_b, topp, &pos, &hs, &total)) {
+          have = true;
+          last_idx = pos;
+          cum = hs;
+        } else if (bin_lo == 0) {
+          // complete candidate set and the sum never exceeded topp: keep everything
+          // (the "in case of rounding errors" branch, sampler.cpp:152)
+          have = true;
+          last_idx = n_b - 1;
+          cum = total;
+        } else {
+          bin_lo = 0;  // the value threshold was too optimistic: take all candidates
+        }
+      }
+      if (n_b <= 0) {
+        token = 0;  // no candidate at all (NaN rows): undefined in the reference
+      } else {
+        const float rr = __fmul_rn(coin, cum);  // sampler.cpp:162
+        int pos;
+        float hs, total;
+        int j = last_idx;
+        if (list_search(sm, listB, n_b, last_idx + 1, rr, &pos, &hs, &total)) j = pos;
+        token = listB[j].idx;
+      }
+    }
+    if (tid == 0) out_ids[r] = (int64_t)token;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Greedy kernel (temperature == 0): sample_argmax (sampler.cpp:44-56). Strict '>' in
+// index order: the lowest index among equal maxima wins, -0 equals +0, a NaN never
+// replaces the running maximum, and a NaN in element 0 is never replaced.
+// ---------------------------------------------------------------------------------------
+template <typename T, bool kRawU16>
+__global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
+    const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
+    int64_t* __restrict__ out_ids) {
+  __shared__ float sv[kWarps];
+  __shared__ int si[kWarps];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* row = logits + r * row_stride;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+    float best = -INFINITY;
+    int besti = 0x7fffffff;  // "nothing better than -inf seen": resolved to the first index below
+    for (int base = 0; base < vocab; base += kTile) {
+      const int i0 = base + tid * kChunk;
+      float x[kChunk];
+      if constexpr (kRawU16) {
+        // sample<uint16_t> compares the raw integers (exact in fp32)
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) x[j] = (i0 + j < vocab) ? (float)row[i0 + j] : 0.0f;
+      } else {
+        load_chunk<T>(row, i0, vocab, vec_ok, x);
+      }
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) {
+        if (i0 + j < vocab && x[j] > best) {
+          best = x[j];
+          besti = i0 + j;
+        }
+      }
+    }
+    // combine: larger value wins, equal values keep the lower index
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, d);
+      if (ov > best || (ov == best && oi < besti)) {
+        best = ov;
+        besti = oi;
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+      sv[warp] = best;
+      si[warp] = besti;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 1; w < kWarps; ++w) {
+        if (sv[w] > best || (sv[w] == best && si[w] < besti)) {
+          best = sv[w];
+          besti = si[w];
+        }
+      }
+      // Sequential semantics at the edges: the scan starts from element 0, so if nothing
+      // compares greater than it (all -inf, or element 0 is NaN) the answer is 0. A running
+      // maximum of -inf is only replaced by something greater, so "all -inf" also yields 0.
+      int ans = besti;
+      float first;
+      if constexpr (kRawU16) {
+        first = (float)row[0];
+      } else {
+        first = to_f32(row[0]);
+      }
+      if (first != first) {
+        ans = 0;  // NaN at index 0 is never replaced
+      } else if (besti == 0x7fffffff) {
+        ans = 0;
+      }
+      out_ids[r] = (int64_t)ans;
+    }
+  }
+}
+
+__global__ void expf_selftest_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n,
+                                     ExpTable table) {
+  __shared__ uint64_t tab[kExpTableSize];
+  if (threadIdx.x < kExpTableSize) tab[threadIdx.x] = table.t[threadIdx.x];
+  __syncthreads();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    y[i] = expf_ref(x[i], tab);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_expf_selftest(const float* x, float* y, int64_t n, const ExpTable& table,
+                                 cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  expf_selftest_kernel<<<(int)blocks, 256, 0, stream>>>(x, y, n, table);
+  return cudaGetLastError();
+}
+
+size_t sampler_scratch_bytes(int vocab, int blocks) {
+  return (size_t)blocks * 2 * (size_t)vocab * sizeof(Entry);
+}
+
+int sampler_threads() { return kThreads; }
+
+template <typename T>
+static cudaError_t launch_sample_t(
+    const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
+    unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
+    const ExpTable& table, int* status, cudaStream_t stream) {
+  sample_rows_kernel<T><<<blocks, kThreads, 0, stream>>>(
+      static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, rng_states, out_ids,
+      static_cast<Entry*>(scratch), table, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sample_rows(
+    int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
+    float topp, unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
+    const ExpTable& table, int* status, cudaStream_t stream) {
+  switch (dtype) {
+    case kDtypeFloat:
+      return launch_sample_t<float>(logits, rows, vocab, row_stride, inv_t, topp, rng_states,
+                                    out_ids, scratch, blocks, table, status, stream);
+    case kDtypeHalf:
+      return launch_sample_t<__half>(logits, rows, vocab, row_stride, inv_t, topp, rng_states,
+                                     out_ids, scratch, blocks, table, status, stream);
+    case kDtypeBFloat16:
+      return launch_sample_t<__nv_bfloat16>(logits, rows, vocab, row_stride, inv_t, topp,
+                                            rng_states, out_ids, scratch, blocks, table, status,
+                                            stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_argmax_rows(
+    int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
+    int blocks, cudaStream_t stream) {
+  switch (dtype) {
+    case kDtypeFloat:
+      argmax_rows_kernel<float, false><<<blocks, kThreads, 0, stream>>>(
+          static_cast<const float*>(logits), rows, vocab, row_stride, out_ids);
+      break;
+    case kDtypeHalf:
+      argmax_rows_kernel<__half, false><<<blocks, kThreads, 0, stream>>>(
+          static_cast<const __half*>(logits), rows, vocab, row_stride, out_ids);
+      break;
+    case kDtypeBFloat16:
+      argmax_rows_kernel<__nv_bfloat16, false><<<blocks, kThreads, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, out_ids);
+      break;
+    case kDtypeUInt16:
+      argmax_rows_kernel<unsigned short, true><<<blocks, kThreads, 0, stream>>>(
+          static_cast<const unsigned short*>(logits), rows, vocab, row_stride, out_ids);
+      break;
+    default:
+      return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+int sample_kernel_max_blocks_per_sm(int dtype) {
+  int n = 0;
+  cudaError_t e;
+  switch (dtype) {
+    case kDtypeFloat:
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float>, kThreads, 0);
+      break;
+    case kDtypeHalf:
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half>, kThreads, 0);
+      break;
+    default:
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16>, kThreads, 0);
+      break;
+  }
+  if (e != cudaSuccess || n < 1) n = 1;
+  return n;
+}
+
+}  // namespace etb200

@@ -1,0 +1,46 @@
+// Launch interface of the sampling kernels (sampler_kernels.cu). Host-only declarations;
+// the C ABI in c_api.cu is the only caller.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "exact_math.cuh"
+
+namespace etb200 {
+
+// dtype codes = the reference's ScalarType numbering
+// (runtime/core/portable_type/scalar_type.h:98-125)
+constexpr int kDtypeHalf = 5;
+constexpr int kDtypeFloat = 6;
+constexpr int kDtypeBFloat16 = 15;
+constexpr int kDtypeUInt16 = 27;
+
+// Bytes of candidate-list scratch the sampling kernel needs when launched with `blocks`
+// thread blocks on rows of `vocab` logits.
+size_t sampler_scratch_bytes(int vocab, int blocks);
+
+// Resident thread blocks per SM of the sampling kernel for a dtype (occupancy query).
+int sample_kernel_max_blocks_per_sm(int dtype);
+
+int sampler_threads();
+
+// temperature != 0: multinomial (topp outside (0,1)) or top-p sampling of every row.
+// rng_states[r] is advanced once per row; out_ids[r] receives the token.
+cudaError_t launch_sample_rows(
+    int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
+    float topp, unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
+    const ExpTable& table, int* status, cudaStream_t stream);
+
+// temperature == 0: greedy argmax of every row.
+cudaError_t launch_argmax_rows(
+    int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
+    int blocks, cudaStream_t stream);
+
+// y[i] = expf_ref(x[i]) on the device, for x <= 0: lets a test compare the device
+// exponential with the host libm.
+cudaError_t launch_expf_selftest(const float* x, float* y, int64_t n, const ExpTable& table,
+                                 cudaStream_t stream);
+
+}  // namespace etb200

@@ -1,0 +1,211 @@
+"""Python mirror of the reference's sampling interface, backed by the CUDA library.
+
+``Sampler`` keeps the constructor and methods of ``executorch::extension::llm::Sampler``
+(extension/llm/sampler/sampler.h:37-83) and adds the batched ``sample_rows``;
+``sample_from_logits`` and ``logits_to_token`` mirror extension/llm/sampler/util.h:25-71.
+Every call goes through the C ABI declared in include/etb200_sampler.h.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+
+K_TOPP = 0.9  # kTopp, sampler.h:29
+
+_TORCH_DTYPES = {
+    torch.float16: _lib.DTYPE_HALF,
+    torch.float32: _lib.DTYPE_FLOAT,
+    torch.bfloat16: _lib.DTYPE_BFLOAT16,
+    torch.uint16: _lib.DTYPE_UINT16,
+}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _TORCH_DTYPES[t.dtype]
+    except KeyError:
+        # sample_from_logits aborts on other dtypes (util.h:30-34)
+        raise _lib.SamplerError(_lib.NOT_SUPPORTED, f"unsupported logits dtype {t.dtype}") from None
+
+
+def seeds_to_states(seeds, device) -> torch.Tensor:
+    """Per-row xorshift64* states initialised from per-row seeds (uint64 bit patterns kept
+    in an int64 tensor, which is what torch can index and copy)."""
+    a = np.ascontiguousarray(np.asarray(seeds, dtype=np.uint64)).view(np.int64)
+    return torch.from_numpy(a.copy()).to(device)
+
+
+class Sampler:
+    """``Sampler(vocab_size, temperature, topp, rng_seed)`` or ``Sampler(vocab_size,
+    temperature)`` (top-p 0.9 and a wall-clock seed), as sampler.cpp:173-187."""
+
+    def __init__(self, vocab_size: int, temperature: float, topp: float | None = None,
+                 rng_seed: int | None = None, device: int | torch.device | None = None):
+        self._h = C.c_void_p()
+        lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: the B200 sampler has no CPU path")
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        self.vocab_size = int(vocab_size)
+        idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        if (topp is None) != (rng_seed is None):
+            raise TypeError("pass both topp and rng_seed (4-argument form) or neither (2-argument form)")
+        if topp is None:
+            _lib.check(lib.etb200_sampler_create_default(self.vocab_size, temperature, idx, C.byref(self._h)))
+        else:
+            _lib.check(lib.etb200_sampler_create(
+                self.vocab_size, temperature, topp, C.c_uint64(rng_seed & (2**64 - 1)), idx, C.byref(self._h)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.load().etb200_sampler_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- sampler.h:48-60
+    def set_temperature(self, temperature: float) -> None:
+        _lib.check(_lib.load().etb200_sampler_set_temperature(self._h, temperature))
+
+    def set_topk(self, topk: int) -> None:
+        _lib.check(_lib.load().etb200_sampler_set_topk(self._h, topk))
+
+    @property
+    def rng_state(self) -> int:
+        out = C.c_uint64(0)
+        _lib.check(_lib.load().etb200_sampler_get_rng_state(self._h, C.byref(out)))
+        return int(out.value)
+
+    @rng_state.setter
+    def rng_state(self, value: int) -> None:
+        _lib.check(_lib.load().etb200_sampler_set_rng_state(self._h, C.c_uint64(value & (2**64 - 1))))
+
+    @property
+    def launch_count(self) -> int:
+        out = C.c_uint64(0)
+        _lib.check(_lib.load().etb200_sampler_launch_count(self._h, C.byref(out)))
+        return int(out.value)
+
+    def _stream(self) -> C.c_void_p:
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check_rows(self, logits: torch.Tensor) -> None:
+        if logits.dim() != 2:
+            raise ValueError(f"expected [rows, vocab] logits, got shape {tuple(logits.shape)}")
+        if logits.shape[1] != self.vocab_size:
+            raise ValueError(f"last dimension {logits.shape[1]} != vocab_size {self.vocab_size}")
+        if logits.stride(1) != 1:
+            raise ValueError("logits rows must be contiguous (stride 1 in the vocab dimension)")
+
+    def sample(self, logits: torch.Tensor) -> int:
+        """``int32_t Sampler::sample(T* logits)`` on one row of device logits; uses and
+        advances the sampler's own RNG state."""
+        if logits.device.type != "cuda":
+            raise ValueError("sample() takes device logits; use sample_rows_host for host memory")
+        row = logits.reshape(-1)
+        if row.numel() != self.vocab_size or row.stride(0) != 1:
+            raise ValueError("sample() needs one contiguous row of vocab_size logits")
+        out = C.c_int32(-1)
+        _lib.check(_lib.load().etb200_sampler_sample(
+            self._h, C.c_void_p(row.data_ptr()), _dtype_code(row), self._stream(), C.byref(out)))
+        return int(out.value)
+
+    def sample_rows(self, logits: torch.Tensor, rng_states: torch.Tensor | None = None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        """Samples every row of ``logits`` ([rows, vocab], device). ``rng_states`` is an int64
+        device tensor of per-row xorshift64* states, advanced in place (not needed at
+        temperature 0). Asynchronous on the current stream; returns int64 ids on device."""
+        self._check_rows(logits)
+        if logits.device != self.device:
+            raise ValueError(f"logits on {logits.device}, sampler on {self.device}")
+        rows = logits.shape[0]
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int64, device=self.device)
+        elif out.dtype != torch.int64 or out.numel() < rows or not out.is_contiguous():
+            raise ValueError("out must be a contiguous int64 tensor with one element per row")
+        states_ptr = C.c_void_p(0)
+        if rng_states is not None:
+            if (rng_states.dtype != torch.int64 or rng_states.numel() != rows
+                    or not rng_states.is_contiguous() or rng_states.device != self.device):
+                raise ValueError("rng_states must be a contiguous int64 device tensor, one per row")
+            states_ptr = C.c_void_p(rng_states.data_ptr())
+        _lib.check(_lib.load().etb200_sampler_sample_rows(
+            self._h, C.c_void_p(logits.data_ptr()), _dtype_code(logits), rows, logits.stride(0),
+            states_ptr, C.c_void_p(out.data_ptr()), self._stream()))
+        return out
+
+    def sample_rows_host(self, logits, rng_states: np.ndarray | None, dtype: str | None = None
+                         ) -> np.ndarray:
+        """Host-memory entry: ``logits`` is a [rows, vocab] CPU tensor or numpy array
+        (uint16 payloads need ``dtype`` 'bf16', 'fp16' or 'u16'); ``rng_states`` a uint64 numpy
+        array advanced in place. Copies in, samples, copies ids back, synchronises."""
+        if isinstance(logits, torch.Tensor):
+            code = _dtype_code(logits)
+            if logits.dim() != 2 or logits.shape[1] != self.vocab_size or logits.stride(1) != 1:
+                raise ValueError("expected contiguous [rows, vocab] host logits")
+            ptr, rows, stride = logits.data_ptr(), logits.shape[0], logits.stride(0)
+        else:
+            a = logits
+            if a.ndim != 2 or a.shape[1] != self.vocab_size or not a.flags.c_contiguous:
+                raise ValueError("expected C-contiguous [rows, vocab] host logits")
+            if a.dtype == np.float32:
+                code = _lib.DTYPE_FLOAT
+            elif a.dtype == np.float16:
+                code = _lib.DTYPE_HALF
+            elif a.dtype == np.uint16:
+                code = {"bf16": _lib.DTYPE_BFLOAT16, "fp16": _lib.DTYPE_HALF, "u16": _lib.DTYPE_UINT16}[dtype or "bf16"]
+            else:
+                raise _lib.SamplerError(_lib.NOT_SUPPORTED, f"unsupported logits dtype {a.dtype}")
+            ptr, rows, stride = a.ctypes.data, a.shape[0], a.shape[1]
+        out = np.empty(rows, dtype=np.int64)
+        sp = C.c_void_p(0)
+        if rng_states is not None:
+            if rng_states.dtype != np.uint64 or rng_states.shape != (rows,) or not rng_states.flags.c_contiguous:
+                raise ValueError("rng_states must be a contiguous uint64 array, one per row")
+            sp = C.c_void_p(rng_states.ctypes.data)
+        _lib.check(_lib.load().etb200_sampler_sample_rows_host(
+            self._h, C.c_void_p(ptr), code, rows, stride, sp, C.c_void_p(out.ctypes.data), self._stream()))
+        return out
+
+
+def sample_from_logits(logits_tensor: torch.Tensor, sampler: Sampler) -> int:
+    """util.h:25-55: the vocabulary is the last dimension; a rank-3 [B, S, V] tensor is
+    sampled at the last sequence position of batch 0."""
+    vocab = logits_tensor.shape[-1]
+    t = logits_tensor
+    if t.dim() == 3:
+        t = t[0, t.shape[1] - 1]
+    else:
+        t = t.reshape(-1)[:vocab]
+    return sampler.sample(t)
+
+
+def sample_all_from_logits(logits_tensor: torch.Tensor, sampler: Sampler,
+                           rng_states: torch.Tensor | None = None) -> torch.Tensor:
+    """Batched form of sample_from_logits: every batch row ([B, V], or the last position of
+    each batch of [B, S, V]) is sampled; the reference reads batch 0 only (util.h:48-51)."""
+    t = logits_tensor
+    if t.dim() == 3:
+        t = t[:, t.shape[1] - 1, :]
+    elif t.dim() == 1:
+        t = t[None, :]
+    return sampler.sample_rows(t, rng_states)
+
+
+def logits_to_token(logits_tensor: torch.Tensor, temperature: float = 0.0) -> int:
+    """util.h:64-71: a temporary two-argument Sampler (top-p 0.9, wall-clock seed)."""
+    s = Sampler(logits_tensor.shape[-1], temperature, device=logits_tensor.device)
+    try:
+        return sample_from_logits(logits_tensor, s)
+    finally:
+        s.close()

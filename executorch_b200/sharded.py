@@ -1,0 +1,60 @@
+"""Row-sharded sampling across the GPUs of one node: one process per GPU, rows split in
+contiguous blocks, and one all-gather of the sampled int64 ids (8 bytes per row) as the
+only exchange. The reference has no multi-device path; rows are independent, so sharding
+changes no result: row r draws from state r whichever rank owns it."""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous block of rows owned by ``rank``: (first_row, count). Blocks are equal
+    when ``world`` divides ``rows``; otherwise the first ``rows % world`` ranks get one more."""
+    if world < 1 or not (0 <= rank < world) or rows < 0:
+        raise ValueError(f"bad shard request rows={rows} rank={rank} world={world}")
+    base, extra = divmod(rows, world)
+    start = rank * base + min(rank, extra)
+    return start, base + (1 if rank < extra else 0)
+
+
+class ShardedSampler:
+    """Samples this rank's rows with ``local_sample`` and gathers all ids on every rank.
+
+    ``local_sample(logits, rng_states) -> int64 ids`` is normally ``Sampler.sample_rows``;
+    tests inject a CPU stand-in to exercise the exchange with the gloo backend."""
+
+    def __init__(self, local_sample: Callable[[torch.Tensor, torch.Tensor | None], torch.Tensor],
+                 total_rows: int, group=None):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.local_sample = local_sample
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.total_rows = total_rows
+        self.start, self.count = shard_rows(total_rows, self.rank, self.world)
+        self.even = total_rows % self.world == 0
+
+    def sample_rows(self, local_logits: torch.Tensor, local_states: torch.Tensor | None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        if local_logits.shape[0] != self.count:
+            raise ValueError(f"rank {self.rank} owns {self.count} rows, got {local_logits.shape[0]}")
+        ids = self.local_sample(local_logits, local_states)
+        if out is None:
+            out = torch.empty(self.total_rows, dtype=torch.int64, device=ids.device)
+        if self.even:
+            dist.all_gather_into_tensor(out, ids, group=self.group)
+        else:
+            # ragged shards: pad to the largest block, gather, then drop the padding
+            width = -(-self.total_rows // self.world)
+            padded = torch.zeros(width, dtype=torch.int64, device=ids.device)
+            padded[: self.count] = ids
+            gathered = torch.empty(width * self.world, dtype=torch.int64, device=ids.device)
+            dist.all_gather_into_tensor(gathered, padded, group=self.group)
+            for r in range(self.world):
+                s, c = shard_rows(self.total_rows, r, self.world)
+                out[s:s + c] = gathered[r * width: r * width + c]
+        return out

@@ -1,0 +1,147 @@
+/*
+ * C ABI of the B200 token sampler: a drop-in for the sampling step of ExecuTorch's LLM
+ * runner, i.e. executorch::extension::llm::Sampler (extension/llm/sampler/sampler.h:37-83)
+ * as called through sample_from_logits / logits_to_token (extension/llm/sampler/util.h:25-71)
+ * by TextDecoderRunner::logits_to_token (extension/llm/runner/text_decoder_runner.h:84-94).
+ *
+ * Conventions (the ones of the reference's CUDA shims, backends/cuda/runtime/shims/rand.h:
+ * extern "C", error code returned, results through out-pointers, no exceptions, no C++
+ * types):
+ *  - every function returns an etb200_error_t whose values are the reference's
+ *    executorch::runtime::Error codes (runtime/core/error.h:29-100);
+ *  - dtype arguments use the reference's ScalarType numbering
+ *    (runtime/core/portable_type/scalar_type.h:98-125): Half 5, Float 6, BFloat16 15,
+ *    UInt16 27;
+ *  - `stream` is a cudaStream_t passed as void* (the caller's stream, as in
+ *    extension/cuda/caller_stream.h); work is enqueued on it and, unless stated otherwise,
+ *    NOT synchronised;
+ *  - logits are read in place and never modified (the reference overwrites them with
+ *    probabilities, sampler.cpp:231-235; its callers never read them again);
+ *  - 16-bit logits are sampled with the reference's float arithmetic on their exact fp32
+ *    upcast (what the reference's newer runners do,
+ *    examples/models/gemma4/runner/gemma4_runner.cpp:166-182,308);
+ *  - a sampler handle, like the reference's Sampler, is not thread-safe: callers serialise
+ *    calls on one handle (text_decoder_runner.h:81-82); distinct handles are independent.
+ *
+ * There is no CPU fallback: without a CUDA device every call fails with an error code.
+ */
+#ifndef ETB200_SAMPLER_H_
+#define ETB200_SAMPLER_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define ETB200_EXPORT __attribute__((visibility("default")))
+#else
+#define ETB200_EXPORT
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint32_t etb200_error_t;
+
+/* executorch::runtime::Error values used by this library (runtime/core/error.h:29-100) */
+enum {
+  ETB200_OK = 0x00,
+  ETB200_INTERNAL = 0x01,
+  ETB200_INVALID_STATE = 0x02,
+  ETB200_NOT_SUPPORTED = 0x10,
+  ETB200_INVALID_ARGUMENT = 0x12,
+  ETB200_MEMORY_ALLOCATION_FAILED = 0x21
+};
+
+/* ScalarType codes accepted for logits (scalar_type.h:98-125); the same four types that
+ * sample_from_logits dispatches on (util.h:36-53). */
+enum {
+  ETB200_DTYPE_HALF = 5,
+  ETB200_DTYPE_FLOAT = 6,
+  ETB200_DTYPE_BFLOAT16 = 15,
+  ETB200_DTYPE_UINT16 = 27
+};
+
+typedef struct etb200_sampler etb200_sampler_t;
+
+/* Sampler::Sampler(vocab_size, temperature, topp, rng_seed), sampler.cpp:173-181.
+ * temperature 0 selects greedy argmax; it is not clamped here (a negative value keeps
+ * 1/temperature, as in the reference). `device` is the CUDA device ordinal that owns the
+ * handle's state and scratch memory. */
+ETB200_EXPORT etb200_error_t etb200_sampler_create(
+    int32_t vocab_size, float temperature, float topp, uint64_t rng_seed, int32_t device,
+    etb200_sampler_t** out_handle);
+
+/* Sampler::Sampler(vocab_size, temperature), sampler.cpp:183-187: topp = 0.9 (kTopp,
+ * sampler.h:29) and the seed is the wall-clock time in seconds. */
+ETB200_EXPORT etb200_error_t etb200_sampler_create_default(
+    int32_t vocab_size, float temperature, int32_t device, etb200_sampler_t** out_handle);
+
+/* ~Sampler: frees the handle's device memory (synchronises the device). */
+ETB200_EXPORT etb200_error_t etb200_sampler_destroy(etb200_sampler_t* handle);
+
+/* Sampler::set_temperature, sampler.h:48-53: negative values are reset to 0. */
+ETB200_EXPORT etb200_error_t etb200_sampler_set_temperature(
+    etb200_sampler_t* handle, float temperature);
+
+/* Sampler::set_topk, sampler.h:58-60. k <= 0 or k >= vocab_size disables top-k. */
+ETB200_EXPORT etb200_error_t etb200_sampler_set_topk(etb200_sampler_t* handle, int32_t topk);
+
+/* Reads back / replaces the handle's own xorshift64* state (Sampler::rng_state_,
+ * sampler.h:82), so that a caller can checkpoint and resume a decode loop. Synchronises. */
+ETB200_EXPORT etb200_error_t etb200_sampler_get_rng_state(
+    etb200_sampler_t* handle, uint64_t* out_state);
+ETB200_EXPORT etb200_error_t etb200_sampler_set_rng_state(
+    etb200_sampler_t* handle, uint64_t state);
+
+/* int32_t Sampler::sample<T>(T* logits), sampler.cpp:222-251, for ONE row of vocab_size
+ * logits in device memory. Uses and advances the handle's own RNG state. Synchronises the
+ * stream and returns the token through out_token (host memory). */
+ETB200_EXPORT etb200_error_t etb200_sampler_sample(
+    etb200_sampler_t* handle, const void* logits_device, int32_t dtype, void* stream,
+    int32_t* out_token);
+
+/* Batched extension of Sampler::sample: samples `rows` independent rows
+ * (row r starts at logits + r * row_stride_elems elements; a stride of 0 samples the same
+ * row `rows` times, once per RNG state) with one launch.
+ *   rng_states: device array of `rows` xorshift64* states, one per row, read and advanced
+ *               once per row exactly like Sampler::rng_state_ (sampler.cpp:210-220,237);
+ *               initialise it with the per-row seeds. Not touched when temperature == 0.
+ *               May be NULL only when rows == 1 (the handle's own state is used).
+ *   out_ids:    device array of `rows` int64 token ids.
+ * The first top-p call on a handle (and any later call that needs more) allocates the
+ * handle's candidate-list scratch memory with cudaMalloc. */
+ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows(
+    etb200_sampler_t* handle, const void* logits_device, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* out_ids_device,
+    void* stream);
+
+/* Same as etb200_sampler_sample_rows for callers whose logits live in HOST memory (what
+ * sample_from_logits receives from a CPU tensor, util.h:25-55): copies the rows to the
+ * device, samples, copies ids and advanced states back, and synchronises the stream.
+ * rng_states_host must hold `rows` states (ignored when temperature == 0). */
+ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_host(
+    etb200_sampler_t* handle, const void* logits_host, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_host, int64_t* out_ids_host, void* stream);
+
+/* Diagnostic: y[i] = the library's device expf(x[i]) for n floats x <= 0 in device memory.
+ * The sampler's results depend on expf matching the host libm that the reference calls
+ * (sampler.cpp:201) bit for bit; this lets a test verify that on the machine at hand. */
+ETB200_EXPORT etb200_error_t etb200_selftest_expf(
+    const float* x_device, float* y_device, int64_t n, void* stream);
+
+/* Number of kernels this library has launched through `handle` so far. */
+ETB200_EXPORT etb200_error_t etb200_sampler_launch_count(
+    etb200_sampler_t* handle, uint64_t* out_count);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+ETB200_EXPORT const char* etb200_last_error_message(void);
+
+/* ABI revision of this header. */
+ETB200_EXPORT uint32_t etb200_sampler_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ETB200_SAMPLER_H_ */
