@@ -259,6 +259,25 @@ ETB_HD void seq_push_scaled(SeqSummary* s, float v, float inv_u) {
   if (s->a1 > kSeqSat) s->a1 = kSeqSat;
 }
 
+// Tie-free fast variant of seq_push_scaled: adds round_half_even(v / u) to *acc and returns
+// true when v / u lies exactly half-way between two integers (then the caller must redo the
+// chunk with the two-parity functions, because the result depends on the parity of N).
+// v / u is clamped to 2^24; any chunk containing such a term leaves the binade anyway.
+ETB_HD bool seq_push_fast(int* acc, float v, float inv_u) {
+#if defined(__CUDA_ARCH__)
+  const float t = fminf(__fmul_rn(v, inv_u), 16777216.0f);
+  const float tm = __fadd_rn(t, 8388608.0f);  // 2^23: the sum's low bits are the rounded t
+  const float d = __fsub_rn(t, __fsub_rn(tm, 8388608.0f));
+#else
+  float t = v * inv_u;
+  t = t < 16777216.0f ? t : 16777216.0f;
+  const float tm = t + 8388608.0f;
+  const float d = t - (tm - 8388608.0f);
+#endif
+  *acc += (int)(f32_bits(tm) - 0x4B000000u);
+  return d == 0.5f || d == -0.5f;
+}
+
 // 2^(150 - kb) as a float when representable as a normal number (kb in [24, 150+126]); the
 // caller uses seq_push_scaled only for kb >= 27.
 ETB_HD float seq_inv_u(int kb) {

@@ -8,7 +8,10 @@
 //
 //   1. max of the temperature-scaled logits                      (HBM read of the row)
 //   2. e_i = expf(x_i - max), exact sequential-order float sum S (row re-read, L2 resident);
-//      top-p also appends (e_i, i) of every possible nucleus member to a per-block list
+//      top-p also appends (e_i, i) of every possible nucleus member to a per-block list.
+//      For bf16 logits e_i comes from a per-row table in shared memory indexed by the
+//      logit's bit pattern (a bf16 row has few distinct values), so expf runs once per
+//      table entry instead of once per logit.
 //   3a. multinomial: exact running cdf of e_i / S in index order until it exceeds the coin
 //   3b. top-p: pick a value threshold from a histogram of the list, compact the survivors
 //       with p_i = e_i / S >= cutoff, LSD-radix sort them (probability descending, stable =
@@ -21,6 +24,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "exact_math.cuh"
 #include "sampler_kernels.cuh"
 
@@ -30,21 +35,35 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kChunk = 8;                   // consecutive logits per thread per tile
+constexpr int kChunk = 16;                  // consecutive logits per thread per tile
 constexpr int kTile = kThreads * kChunk;    // logits per tile
+constexpr int kHead = 256;                  // leading terms of a sum that one thread adds sequentially
 constexpr int kHistShift = 19;              // histogram bin = float bits >> 19 (exponent + 4 mantissa bits)
 constexpr int kHistBins = (0x3F800000 >> kHistShift) + 2;  // values in (0, 1]
 constexpr int kRadixBits = 8;
 constexpr int kRadix = 1 << kRadixBits;
+constexpr int kFastSat = 1 << 25;           // per-thread clamp of chunk summaries
+
+// bf16 table of e by logit bit pattern: both signs, |logit| in [2^-16, 2^8), plus +0 and -0.
+// Anything else (tiny, huge, infinite, NaN) is rare and computed directly.
+constexpr int kLutExpLo = 127 - 16;
+constexpr int kLutExpHi = 127 + 8;
+constexpr int kLutPerSign = (kLutExpHi - kLutExpLo) * 128;
+constexpr int kLutSize = 2 * kLutPerSign + 2;
 
 struct Entry {
   uint32_t key;  // float bits of e_i (list A) or p_i (sorted lists); positive floats order like integers
   int32_t idx;   // token index
 };
 
+template <bool kLut>
 struct __align__(16) Shared {
+  static constexpr bool kHasLut = kLut;
   uint64_t exp_tab[kExpTableSize];
+  float lut[kLut ? kLutSize : 2];
+  float head[kHead];
   SeqSummary wsum[kWarps];
+  int wsum_i[kWarps];
   int wcnt[2][kWarps];
   float redf[kWarps];
   int redi[kWarps];
@@ -72,30 +91,8 @@ __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// Loads kChunk consecutive logits starting at element i0 of a row, upcast exactly to fp32.
-// Elements at or beyond `vocab` are returned as 0 and must be masked by the caller.
-template <typename T>
-__device__ __forceinline__ void load_chunk(
-    const T* __restrict__ row, int i0, int vocab, bool vec_ok, float (&x)[kChunk]) {
-  constexpr int kPerVec = 16 / sizeof(T);
-  if (vec_ok && i0 + kChunk <= vocab) {
-#pragma unroll
-    for (int v = 0; v < kChunk / kPerVec; ++v) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + i0) + v);
-      const T* p = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-      for (int j = 0; j < kPerVec; ++j) x[v * kPerVec + j] = to_f32(p[j]);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < kChunk; ++j) {
-      const int i = i0 + j;
-      x[j] = (i < vocab) ? to_f32(row[i]) : 0.0f;
-    }
-  }
-}
-
-__device__ __forceinline__ float block_max(Shared& sm, float v) {
+template <typename S>
+__device__ __forceinline__ float block_max(S& sm, float v) {
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
   __syncthreads();
@@ -108,7 +105,8 @@ __device__ __forceinline__ float block_max(Shared& sm, float v) {
 }
 
 // Exclusive block-wide prefix count of a per-thread count; *total gets the block sum.
-__device__ __forceinline__ int block_excl_count(Shared& sm, int cnt, int* total) {
+template <typename S>
+__device__ __forceinline__ int block_excl_count(S& sm, int cnt, int* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int inc = cnt;
 #pragma unroll
@@ -135,15 +133,20 @@ __device__ __forceinline__ int block_excl_count(Shared& sm, int cnt, int* total)
 // v[] that follow the terms of threads 0..t-1. `s` is the running sum in front of the
 // tile on entry and behind it on return (block-uniform).
 //
+// Each round summarises every thread's chunk in the binade of s. The common case has no
+// exact half-way tie anywhere in the tile: then a chunk's summary is one integer and the
+// block scan is a plain integer prefix sum. A tie anywhere switches the round to the
+// two-parity summaries of exact_math.cuh.
+//
 // With kSearch, also looks for the first term after which the running sum exceeds `thr`
-// (terms at position >= limit, counted from pos0 of thread 0's first term, are padding
-// zeros and never match); on a match returns true with the position in *hit_pos and the
-// sum reached there in *hit_sum (block-uniform), and `s` is then not meaningful.
+// (terms at position >= limit, counted from pos0 of thread 0's first term, must be zero
+// padding); on a match returns true with the position in *hit_pos and the sum reached
+// there in *hit_sum (block-uniform), and `s` is then not meaningful.
 // ---------------------------------------------------------------------------------------
-template <bool kSearch>
+template <bool kSearch, typename S>
 __device__ __forceinline__ bool seqsum_tile(
-    Shared& sm, const float (&v)[kChunk], float& s, float thr, int pos0, int limit,
-    int* hit_pos, float* hit_sum) {
+    S& sm, const float (&v)[kChunk], float& s, float thr, int pos0, int limit, int* hit_pos,
+    float* hit_sum) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int consumed = 0;
   while (true) {
@@ -151,56 +154,99 @@ __device__ __forceinline__ bool seqsum_tile(
     const int n_s = seq_n(s);
     SeqSummary mine;
     seq_identity(&mine);
-    if (tid >= consumed) {
+    const bool active = tid >= consumed;
+    if (active) {
       if (kb >= 27) {
+        // v / u by an exact power-of-two scaling; adding 2^23 rounds it to an integer
+        // (half to even) that can be read off the sum's bit pattern
         const float inv_u = seq_inv_u(kb);
+        int acc = 0;
+        bool tie = false;
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) seq_push_scaled(&mine, v[j], inv_u);
+        for (int j = 0; j < kChunk; ++j) tie = seq_push_fast(&acc, v[j], inv_u) || tie;
+        acc = acc < kFastSat ? acc : kFastSat;
+        mine.a0 = acc;
+        mine.a1 = acc;
+        if (tie) {
+          seq_identity(&mine);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) seq_push_scaled(&mine, v[j], inv_u);
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) seq_push(&mine, v[j], kb);
       }
+      if (mine.a0 > kFastSat) mine.a0 = kFastSat;
+      if (mine.a1 > kFastSat) mine.a1 = kFastSat;
     }
-    SeqSummary inc = mine;
+    // barrier: also separates this round from the previous readers of the shared slots
+    const int two_parity = __syncthreads_or(mine.a0 != mine.a1);
+    int n_in, n_out, n_total;
+    if (!two_parity) {
+      int inc = mine.a0;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      SeqSummary o;
-      o.a0 = __shfl_up_sync(0xffffffffu, inc.a0, d);
-      o.a1 = __shfl_up_sync(0xffffffffu, inc.a1, d);
-      if (lane >= d) inc = seq_compose(o, inc);
-    }
-    SeqSummary excl;
-    excl.a0 = __shfl_up_sync(0xffffffffu, inc.a0, 1);
-    excl.a1 = __shfl_up_sync(0xffffffffu, inc.a1, 1);
-    if (lane == 0) seq_identity(&excl);
-    __syncthreads();  // previous readers of wsum / first / s_bcast are done
-    if (lane == 31) sm.wsum[warp] = inc;
-    if (tid == 0) {
-      sm.first = kThreads;
-      sm.hit_found = 0;
-    }
-    __syncthreads();
-    // every warp redundantly scans the kWarps warp totals with shuffles
-    SeqSummary wt;
-    seq_identity(&wt);
-    if (lane < kWarps) wt = sm.wsum[lane];
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      if (lane == 31) sm.wsum_i[warp] = inc < kFastSat ? inc : kFastSat;
+      if (tid == 0) {
+        sm.first = kThreads;
+        sm.hit_found = 0;
+      }
+      __syncthreads();
+      int wt = (lane < kWarps) ? sm.wsum_i[lane] : 0;
 #pragma unroll
-    for (int d = 1; d < kWarps; d <<= 1) {
-      SeqSummary o;
-      o.a0 = __shfl_up_sync(0xffffffffu, wt.a0, d);
-      o.a1 = __shfl_up_sync(0xffffffffu, wt.a1, d);
-      if (lane >= d) wt = seq_compose(o, wt);
+      for (int d = 1; d < kWarps; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, wt, d);
+        if (lane >= d) wt += o;
+      }
+      int pre = __shfl_sync(0xffffffffu, wt, warp > 0 ? warp - 1 : 0);
+      if (warp == 0) pre = 0;
+      n_total = n_s + __shfl_sync(0xffffffffu, wt, kWarps - 1);
+      n_in = n_s + pre + (inc - mine.a0);
+      n_out = n_in + mine.a0;
+    } else {
+      SeqSummary inc = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        SeqSummary o;
+        o.a0 = __shfl_up_sync(0xffffffffu, inc.a0, d);
+        o.a1 = __shfl_up_sync(0xffffffffu, inc.a1, d);
+        if (lane >= d) inc = seq_compose(o, inc);
+      }
+      SeqSummary excl;
+      excl.a0 = __shfl_up_sync(0xffffffffu, inc.a0, 1);
+      excl.a1 = __shfl_up_sync(0xffffffffu, inc.a1, 1);
+      if (lane == 0) seq_identity(&excl);
+      if (lane == 31) sm.wsum[warp] = inc;
+      if (tid == 0) {
+        sm.first = kThreads;
+        sm.hit_found = 0;
+      }
+      __syncthreads();
+      // every warp redundantly scans the kWarps warp totals with shuffles
+      SeqSummary wt;
+      seq_identity(&wt);
+      if (lane < kWarps) wt = sm.wsum[lane];
+#pragma unroll
+      for (int d = 1; d < kWarps; d <<= 1) {
+        SeqSummary o;
+        o.a0 = __shfl_up_sync(0xffffffffu, wt.a0, d);
+        o.a1 = __shfl_up_sync(0xffffffffu, wt.a1, d);
+        if (lane >= d) wt = seq_compose(o, wt);
+      }
+      SeqSummary pre, total;
+      pre.a0 = __shfl_sync(0xffffffffu, wt.a0, warp > 0 ? warp - 1 : 0);
+      pre.a1 = __shfl_sync(0xffffffffu, wt.a1, warp > 0 ? warp - 1 : 0);
+      if (warp == 0) seq_identity(&pre);
+      total.a0 = __shfl_sync(0xffffffffu, wt.a0, kWarps - 1);
+      total.a1 = __shfl_sync(0xffffffffu, wt.a1, kWarps - 1);
+      pre = seq_compose(pre, excl);
+      n_in = seq_apply(n_s, pre);
+      n_out = seq_apply(n_in, mine);
+      n_total = seq_apply(n_s, total);
     }
-    SeqSummary pre, total;
-    pre.a0 = __shfl_sync(0xffffffffu, wt.a0, warp > 0 ? warp - 1 : 0);
-    pre.a1 = __shfl_sync(0xffffffffu, wt.a1, warp > 0 ? warp - 1 : 0);
-    if (warp == 0) seq_identity(&pre);
-    total.a0 = __shfl_sync(0xffffffffu, wt.a0, kWarps - 1);
-    total.a1 = __shfl_sync(0xffffffffu, wt.a1, kWarps - 1);
-    pre = seq_compose(pre, excl);
-    const int n_in = seq_apply(n_s, pre);
-    const int n_out = seq_apply(n_in, mine);
-    const bool active = tid >= consumed;
     bool flag = active && (n_out >= kSeqLimit);
     if (kSearch) {
       if (active && n_out < kSeqLimit && seq_value(kb, n_out) > thr) flag = true;
@@ -211,7 +257,7 @@ __device__ __forceinline__ bool seqsum_tile(
     const int first = sm.first;
     if (first == kThreads) {
       // nothing left the binade: the whole tile is summarised exactly
-      s = seq_value(kb, seq_apply(n_s, total));
+      s = seq_value(kb, n_total);
       return false;
     }
     if (tid == first) {
@@ -246,6 +292,41 @@ __device__ __forceinline__ bool seqsum_tile(
   }
 }
 
+// The first terms of a sum leave a binade every few additions, which would cost one block
+// round each; instead one thread adds the `count` terms staged in sm.head with real float
+// additions. Same contract as seqsum_tile. Callers fill sm.head before the call and need no
+// barrier in between: this function synchronises on entry and on exit.
+template <bool kSearch, typename S>
+__device__ __forceinline__ bool head_sum(
+    S& sm, int count, float& s, float thr, int pos0, int* hit_pos, float* hit_sum) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float acc = s;
+    int found = 0;
+    for (int i = 0; i < count; ++i) {
+      acc = __fadd_rn(acc, sm.head[i]);
+      if (kSearch && acc > thr) {
+        found = 1;
+        sm.hit_idx = pos0 + i;
+        sm.hit_val = acc;
+        break;
+      }
+    }
+    sm.hit_found = found;
+    sm.s_bcast = acc;
+  }
+  __syncthreads();
+  s = sm.s_bcast;
+  bool hit = false;
+  if (kSearch && sm.hit_found) {
+    *hit_pos = sm.hit_idx;
+    *hit_sum = sm.hit_val;
+    hit = true;
+  }
+  __syncthreads();  // the head buffer and the result slots may be reused after this
+  return hit;
+}
+
 // xorshift64* step and 24-bit coin of the reference (sampler.cpp:210-220).
 __device__ __forceinline__ float next_coin(unsigned long long* state) {
   unsigned long long s = *state;
@@ -257,20 +338,135 @@ __device__ __forceinline__ float next_coin(unsigned long long* state) {
   return (float)(u >> 8) / 16777216.0f;
 }
 
-// Scaled logits of one chunk: x = logit * inv_temperature in fp32 (sampler.cpp:231-233).
-template <typename T>
-__device__ __forceinline__ void scaled_chunk(
-    const T* __restrict__ row, int i0, int vocab, bool vec_ok, float inv_t, float (&x)[kChunk]) {
-  load_chunk<T>(row, i0, vocab, vec_ok, x);
+// ---------------------------------------------------------------------------------------
+// Per-row element math: e = expf(logit * inv_t - mx) (sampler.cpp:231-233 and :201), or
+// e / S once the sum is known (sampler.cpp:205-207) when `probs` is set.
+// ---------------------------------------------------------------------------------------
+template <typename T, typename S>
+struct RowMath {
+  const T* row;
+  int vocab;
+  bool vec_ok;
+  float inv_t;
+  float mx;
+  float sum;   // divisor when probs is set
+  bool probs;
+
+  __device__ __forceinline__ float direct(float logit, const S& sm) const {
+    const float e = expf_ref(__fsub_rn(__fmul_rn(logit, inv_t), mx), sm.exp_tab);
+    return probs ? __fdiv_rn(e, sum) : e;
+  }
+
+  // bf16 bit pattern -> table slot, or -1 when the value is outside the table
+  static __device__ __forceinline__ int lut_slot(uint32_t h) {
+    const uint32_t a = h & 0x7FFFu;
+    const uint32_t sgn = h >> 15;
+    const uint32_t k = a - (uint32_t)(kLutExpLo << 7);
+    if (k < (uint32_t)kLutPerSign) return (int)(k + sgn * kLutPerSign);
+    if (a == 0) return 2 * kLutPerSign + (int)sgn;
+    return -1;
+  }
+
+  static __device__ __forceinline__ uint32_t lut_pattern(int slot) {
+    if (slot >= 2 * kLutPerSign) return (uint32_t)(slot - 2 * kLutPerSign) << 15;
+    const uint32_t sgn = slot >= kLutPerSign ? 1u : 0u;
+    const uint32_t k = (uint32_t)slot - sgn * kLutPerSign;
+    return (sgn << 15) | (k + (uint32_t)(kLutExpLo << 7));
+  }
+
+  // Fills the table for this row (bf16 only): slot -> e, or e / S when probs is set.
+  __device__ __forceinline__ void build_lut(S& sm) const {
+    for (int k = threadIdx.x; k < kLutSize; k += kThreads) {
+      sm.lut[k] = direct(bits_f32(lut_pattern(k) << 16), sm);
+    }
+  }
+
+  __device__ __forceinline__ float from_pattern(uint32_t h, const S& sm) const {
+    const int slot = lut_slot(h);
+    if (slot >= 0) return sm.lut[slot];
+    return direct(bits_f32(h << 16), sm);
+  }
+
+  // One element (used for the sequential head and for ragged edges). 0 beyond the row.
+  __device__ __forceinline__ float at(int i, const S& sm) const {
+    if (i >= vocab) return 0.0f;
+    if constexpr (S::kHasLut) {
+      return from_pattern((uint32_t) reinterpret_cast<const unsigned short*>(row)[i], sm);
+    } else {
+      return direct(to_f32(row[i]), sm);
+    }
+  }
+
+  // kChunk consecutive elements starting at i0.
+  __device__ __forceinline__ void chunk(int i0, const S& sm, float (&e)[kChunk]) const {
+    if (vec_ok && i0 + kChunk <= vocab) {
+      constexpr int kPerVec = 16 / sizeof(T);
 #pragma unroll
-  for (int j = 0; j < kChunk; ++j) x[j] = __fmul_rn(x[j], inv_t);
+      for (int q = 0; q < kChunk / kPerVec; ++q) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + i0) + q);
+        if constexpr (S::kHasLut) {
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            e[q * 8 + 2 * j] = from_pattern(w[j] & 0xFFFFu, sm);
+            e[q * 8 + 2 * j + 1] = from_pattern(w[j] >> 16, sm);
+          }
+        } else {
+          const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int j = 0; j < kPerVec; ++j) e[q * kPerVec + j] = direct(to_f32(p[j]), sm);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) e[j] = at(i0 + j, sm);
+    }
+  }
+};
+
+__device__ __forceinline__ __half2 neg_inf2(__half) {
+  const __half v = __ushort_as_half((unsigned short)0xFC00);
+  return __halves2half2(v, v);
+}
+__device__ __forceinline__ __nv_bfloat162 neg_inf2(__nv_bfloat16) {
+  const __nv_bfloat16 v = __ushort_as_bfloat16((unsigned short)0xFF80);
+  return __halves2bfloat162(v, v);
+}
+
+// Max over the row of logit * inv_t (softmax, sampler.cpp:191-196).
+template <typename T, typename S>
+__device__ __forceinline__ float row_max_scaled(
+    S& sm, const T* __restrict__ row, int vocab, bool vec_ok, float inv_t) {
+  const int tid = threadIdx.x;
+  if constexpr (sizeof(T) == 2) {
+    if (inv_t > 0.0f) {
+      // x -> fl(x * inv_t) is monotone for inv_t > 0, so the max can be taken on the raw
+      // 16-bit values, two per instruction, and scaled once
+      using T2 = decltype(neg_inf2(T()));
+      const int nvec = vec_ok ? vocab / 8 : 0;
+      T2 acc = neg_inf2(T());
+      for (int q = tid; q < nvec; q += kThreads) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row) + q);
+        const T2* p = reinterpret_cast<const T2*>(&raw);
+        acc = __hmax2(acc, __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3])));
+      }
+      float m = fmaxf(to_f32(acc.x), to_f32(acc.y));
+      for (int i = nvec * 8 + tid; i < vocab; i += kThreads) m = fmaxf(m, to_f32(row[i]));
+      m = block_max(sm, m);
+      return __fmul_rn(m, inv_t);
+    }
+  }
+  float mx = -INFINITY;
+  for (int i = tid; i < vocab; i += kThreads) mx = fmaxf(mx, __fmul_rn(to_f32(row[i]), inv_t));
+  return block_max(sm, mx);
 }
 
 // ---------------------------------------------------------------------------------------
 // Stable LSD radix sort pass over a list of n entries, descending in the 8-bit digit at
 // `shift`. One block; src and dst are distinct global buffers.
 // ---------------------------------------------------------------------------------------
-__device__ void radix_pass_desc(Shared& sm, const Entry* src, Entry* dst, int n, int shift) {
+template <typename S>
+__device__ void radix_pass_desc(S& sm, const Entry* src, Entry* dst, int n, int shift) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   __syncthreads();
   for (int d = tid; d < kRadix; d += kThreads) sm.u.radix.digit[d] = 0;
@@ -335,20 +531,32 @@ __device__ void radix_pass_desc(Shared& sm, const Entry* src, Entry* dst, int n,
 
 // Exact cumulative sum over the key floats of a sorted list, looking for the first
 // position (below `limit`) where it exceeds thr. Returns true with position and sum, else
-// false with the total in *total.
+// false with the total in *total. Short lists are summed sequentially through the head
+// buffer; long ones continue with block-wide tiles.
+template <typename S>
 __device__ bool list_search(
-    Shared& sm, const Entry* list, int n, int limit, float thr, int* pos, float* sum,
-    float* total) {
+    S& sm, const Entry* list, int n, int limit, float thr, int* pos, float* sum, float* total) {
+  const int lim = n < limit ? n : limit;
   float s = 0.0f;
-  for (int base = 0; base < n; base += kTile) {
+  const int seq_end = lim <= 4 * kHead ? lim : kHead;
+  int base = 0;
+  for (; base < seq_end; base += kHead) {
+    const int cnt = (seq_end - base) < kHead ? (seq_end - base) : kHead;
+    __syncthreads();
+    if (threadIdx.x < kHead) {
+      const int i = base + threadIdx.x;
+      sm.head[threadIdx.x] = (i < lim) ? bits_f32(list[i].key) : 0.0f;
+    }
+    if (head_sum<true>(sm, cnt, s, thr, base, pos, sum)) return true;
+  }
+  for (; base < lim; base += kTile) {
     float v[kChunk];
 #pragma unroll
     for (int j = 0; j < kChunk; ++j) {
       const int i = base + threadIdx.x * kChunk + j;
-      v[j] = (i < n && i < limit) ? bits_f32(list[i].key) : 0.0f;
+      v[j] = (i < lim) ? bits_f32(list[i].key) : 0.0f;
     }
-    if (seqsum_tile<true>(sm, v, s, thr, base, limit, pos, sum)) return true;
-    if (base + kTile >= limit) break;  // nothing searchable beyond the limit
+    if (seqsum_tile<true>(sm, v, s, thr, base, lim, pos, sum)) return true;
   }
   *total = s;
   return false;
@@ -358,14 +566,15 @@ __device__ bool list_search(
 // The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
 // otherwise. Follows Sampler::sample<float> (sampler.cpp:222-251).
 // ---------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kLut>
 __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
     float topp, unsigned long long* __restrict__ rng_states, int64_t* __restrict__ out_ids,
     Entry* scratch, ExpTable table, int* __restrict__ status) {
   (void)status;
-  __shared__ Shared sm;
-  const int tid = threadIdx.x;
+  using S = Shared<kLut>;
+  __shared__ S sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
   __syncthreads();
   const bool use_topp = !(topp <= 0.0f || topp >= 1.0f);
@@ -373,25 +582,16 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   Entry* listB = listA + vocab;
 
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    const T* row = logits + r * row_stride;
-    const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+    RowMath<T, S> rm;
+    rm.row = logits + r * row_stride;
+    rm.vocab = vocab;
+    rm.vec_ok = (reinterpret_cast<uintptr_t>(rm.row) & 15u) == 0;
+    rm.inv_t = inv_t;
+    rm.sum = 1.0f;
+    rm.probs = false;
 
-    // ---- pass 1: max of the scaled logits (softmax, sampler.cpp:191-196)
-    float mx = -INFINITY;
-    for (int base = 0; base < vocab; base += kTile) {
-      const int i0 = base + tid * kChunk;
-      float x[kChunk];
-      scaled_chunk<T>(row, i0, vocab, vec_ok, inv_t, x);
-      if (i0 + kChunk <= vocab) {
-#pragma unroll
-        for (int j = 0; j < kChunk; ++j) mx = fmaxf(mx, x[j]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < kChunk; ++j)
-          if (i0 + j < vocab) mx = fmaxf(mx, x[j]);
-      }
-    }
-    mx = block_max(sm, mx);
+    // ---- pass 1: max of the scaled logits
+    rm.mx = row_max_scaled<T>(sm, rm.row, vocab, rm.vec_ok, inv_t);
 
     // the coin is drawn once per sampled row (sampler.cpp:237)
     if (tid == 0) {
@@ -399,42 +599,88 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       sm.misc_f[0] = next_coin(&st);
       rng_states[r] = st;
     }
+    if constexpr (kLut) {
+      rm.build_lut(sm);  // the previous row's readers are behind the barriers of block_max
+    }
 
     // ---- pass 2: e_i = expf(x_i - max) and their float sum in index order
     // (sampler.cpp:198-203). Top-p also lists every entry that can pass the cutoff crop of
     // sampler.cpp:136-143: p_i >= cutoff needs e_i >= cutoff * S and S >= 1 (the maximum
-    // contributes exactly 1), so e_i >= cutoff * (1 - 2^-20) is necessary.
+    // contributes exactly 1), so e_i >= cutoff * (1 - 1e-6) is necessary.
     const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
     const float e_floor = use_topp ? cutoff * 0.999999f : 0.0f;
     float s = 0.0f;
     int n_a = 0;
-    for (int base = 0; base < vocab; base += kTile) {
-      const int i0 = base + tid * kChunk;
-      float x[kChunk], e[kChunk];
-      scaled_chunk<T>(row, i0, vocab, vec_ok, inv_t, x);
-      int cnt = 0;
-#pragma unroll
-      for (int j = 0; j < kChunk; ++j) {
-        e[j] = (i0 + j < vocab) ? expf_ref(__fsub_rn(x[j], mx), sm.exp_tab) : 0.0f;
-        if (use_topp && (i0 + j < vocab) && e[j] >= e_floor) ++cnt;
-      }
-      if (use_topp) {
-        int tot;
-        int off = n_a + block_excl_count(sm, cnt, &tot);
-#pragma unroll
-        for (int j = 0; j < kChunk; ++j) {
-          if ((i0 + j < vocab) && e[j] >= e_floor) {
+    {
+      // head: the first kHead terms, added by one thread
+      __syncthreads();  // the table is complete
+      const int cnt = vocab < kHead ? vocab : kHead;
+      if (tid < kHead) sm.head[tid] = rm.at(tid, sm);
+      __syncthreads();
+      if (tid == 0) {
+        float acc = 0.0f;
+        int n = 0;
+        for (int i = 0; i < cnt; ++i) {
+          const float e = sm.head[i];
+          acc = __fadd_rn(acc, e);
+          if (use_topp && e >= e_floor) {
             Entry en;
-            en.key = f32_bits(e[j]);
-            en.idx = i0 + j;
-            listA[off++] = en;
+            en.key = f32_bits(e);
+            en.idx = i;
+            listA[n++] = en;
           }
         }
-        n_a += tot;
+        sm.s_bcast = acc;
+        sm.misc_i[0] = n;
+      }
+      __syncthreads();
+      s = sm.s_bcast;
+      n_a = sm.misc_i[0];
+    }
+    int buf = 0;
+    for (int base = kHead; base < vocab; base += kTile) {
+      const int i0 = base + tid * kChunk;
+      float e[kChunk];
+      rm.chunk(i0, sm, e);
+      int cnt = 0, inc = 0;
+      if (use_topp) {
+        // entries beyond the row are 0 and e_floor > 0, so they never count
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) cnt += (e[j] >= e_floor) ? 1 : 0;
+        inc = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += o;
+        }
+        if (lane == 31) sm.wcnt[buf][warp] = inc;  // published by the barriers of seqsum_tile
       }
       int hp;
       float hs;
       seqsum_tile<false>(sm, e, s, 0.0f, base, vocab, &hp, &hs);
+      if (use_topp) {
+        int pre = 0, tot = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const int c = sm.wcnt[buf][w];
+          if (w < warp) pre += c;
+          tot += c;
+        }
+        int off = n_a + pre + inc - cnt;
+        if (cnt > 0) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            if (e[j] >= e_floor) {
+              Entry en;
+              en.key = f32_bits(e[j]);
+              en.idx = i0 + j;
+              listA[off++] = en;
+            }
+          }
+        }
+        n_a += tot;
+        buf ^= 1;
+      }
     }
     const float sum = s;
     __syncthreads();
@@ -444,23 +690,24 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     if (!use_topp) {
       // ---- pass 3a: sample_mult (sampler.cpp:58-70): running float cdf of p_i = e_i / S
       token = vocab - 1;
-      float cdf = 0.0f;
-      for (int base = 0; base < vocab; base += kTile) {
-        const int i0 = base + tid * kChunk;
-        float x[kChunk], p[kChunk];
-        scaled_chunk<T>(row, i0, vocab, vec_ok, inv_t, x);
-#pragma unroll
-        for (int j = 0; j < kChunk; ++j) {
-          const float e = (i0 + j < vocab) ? expf_ref(__fsub_rn(x[j], mx), sm.exp_tab) : 0.0f;
-          p[j] = __fdiv_rn(e, sum);
-        }
-        int hp;
-        float hs;
-        if (seqsum_tile<true>(sm, p, cdf, coin, base, vocab, &hp, &hs)) {
-          token = hp;
-          break;
-        }
+      rm.sum = sum;
+      rm.probs = true;
+      if constexpr (kLut) {
+        rm.build_lut(sm);  // the table now holds probabilities
       }
+      float cdf = 0.0f;
+      int hp;
+      float hs;
+      __syncthreads();
+      const int cnt = vocab < kHead ? vocab : kHead;
+      if (tid < kHead) sm.head[tid] = rm.at(tid, sm);
+      bool hit = head_sum<true>(sm, cnt, cdf, coin, 0, &hp, &hs);
+      for (int base = kHead; base < vocab && !hit; base += kTile) {
+        float p[kChunk];
+        rm.chunk(base + tid * kChunk, sm, p);
+        hit = seqsum_tile<true>(sm, p, cdf, coin, base, vocab, &hp, &hs);
+      }
+      if (hit) token = hp;
     } else {
       // ---- pass 3b: sample_topp (sampler.cpp:122-171)
       __threadfence_block();
@@ -532,30 +779,38 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         // crop, with their probabilities, still in index order
         n_b = 0;
         const uint32_t key_lo = (uint32_t)bin_lo << kHistShift;
-        for (int base = 0; base < n_a; base += kThreads) {
-          const int i = base + tid;
-          Entry en;
-          en.key = 0;
-          en.idx = 0;
-          bool keep = false;
-          if (i < n_a) {
-            en = listA[i];
-            if (en.key >= key_lo) {
-              const float p = __fdiv_rn(bits_f32(en.key), sum);
-              keep = p >= cutoff;
-              en.key = f32_bits(p);
+        constexpr int kPer = 8;
+        for (int base = 0; base < n_a; base += kThreads * kPer) {
+          Entry en[kPer];
+          unsigned keep = 0;
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) {
+            const int i = base + tid * kPer + j;
+            en[j].key = 0;
+            en[j].idx = 0;
+            if (i < n_a) {
+              en[j] = listA[i];
+              if (en[j].key >= key_lo) {
+                const float p = __fdiv_rn(bits_f32(en[j].key), sum);
+                if (p >= cutoff) keep |= 1u << j;
+                en[j].key = f32_bits(p);
+              }
             }
           }
           int tot;
-          const int off = n_b + block_excl_count(sm, keep ? 1 : 0, &tot);
-          if (keep) listB[off] = en;
+          int off = n_b + block_excl_count(sm, __popc(keep), &tot);
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) {
+            if (keep & (1u << j)) listB[off++] = en[j];
+          }
           n_b += tot;
         }
         __threadfence_block();
         __syncthreads();
-        // sort by probability, descending; equal probabilities keep index order.
-        // Passes ping-pong B -> A2 -> B ...; list A must survive for a second attempt, so
-        // the partner buffer is the tail of list A's allocation only when it is free.
+        // sort by probability, descending; equal probabilities keep index order. The passes
+        // ping-pong between list B and free scratch (the tail of list A's buffer, or list A
+        // itself once it is no longer needed); after an even number of passes the result is
+        // back in list B.
         Entry* ping = listB;
         Entry* pong = (n_a + n_b <= vocab) ? listA + n_a : listA;
         for (int pass = 0; pass < 32 / kRadixBits; ++pass) {
@@ -566,10 +821,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
           pong = t;
         }
         __syncthreads();
-        // after an even number of passes the sorted list is back in listB (== ping)
         int pos;
         float hs, total;
-        if (list_search(sm, ping, n_b, n_b, topp, &pos, &hs, &total)) {
+        if (list_search(sm, listB, n_b, n_b, topp, &pos, &hs, &total)) {
           have = true;
           last_idx = pos;
           cum = hs;
@@ -604,6 +858,8 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
 // index order: the lowest index among equal maxima wins, -0 equals +0, a NaN never
 // replaces the running maximum, and a NaN in element 0 is never replaced.
 // ---------------------------------------------------------------------------------------
+constexpr int kArgChunk = 8;
+
 template <typename T, bool kRawU16>
 __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
@@ -616,18 +872,30 @@ __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
     float best = -INFINITY;
     int besti = 0x7fffffff;  // "nothing better than -inf seen": resolved to the first index below
-    for (int base = 0; base < vocab; base += kTile) {
-      const int i0 = base + tid * kChunk;
-      float x[kChunk];
+    for (int base = 0; base < vocab; base += kThreads * kArgChunk) {
+      const int i0 = base + tid * kArgChunk;
+      float x[kArgChunk];
       if constexpr (kRawU16) {
         // sample<uint16_t> compares the raw integers (exact in fp32)
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) x[j] = (i0 + j < vocab) ? (float)row[i0 + j] : 0.0f;
+        for (int j = 0; j < kArgChunk; ++j) x[j] = (i0 + j < vocab) ? (float)row[i0 + j] : 0.0f;
       } else {
-        load_chunk<T>(row, i0, vocab, vec_ok, x);
+        constexpr int kPerVec = 16 / sizeof(T);
+        if (vec_ok && i0 + kArgChunk <= vocab) {
+#pragma unroll
+          for (int q = 0; q < kArgChunk / kPerVec; ++q) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + i0) + q);
+            const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int j = 0; j < kPerVec; ++j) x[q * kPerVec + j] = to_f32(p[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kArgChunk; ++j) x[j] = (i0 + j < vocab) ? to_f32(row[i0 + j]) : 0.0f;
+        }
       }
 #pragma unroll
-      for (int j = 0; j < kChunk; ++j) {
+      for (int j = 0; j < kArgChunk; ++j) {
         if (i0 + j < vocab && x[j] > best) {
           best = x[j];
           besti = i0 + j;
@@ -705,12 +973,12 @@ size_t sampler_scratch_bytes(int vocab, int blocks) {
 
 int sampler_threads() { return kThreads; }
 
-template <typename T>
+template <typename T, bool kLut>
 static cudaError_t launch_sample_t(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
     unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
     const ExpTable& table, int* status, cudaStream_t stream) {
-  sample_rows_kernel<T><<<blocks, kThreads, 0, stream>>>(
+  sample_rows_kernel<T, kLut><<<blocks, kThreads, 0, stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, rng_states, out_ids,
       static_cast<Entry*>(scratch), table, status);
   return cudaGetLastError();
@@ -722,15 +990,16 @@ cudaError_t launch_sample_rows(
     const ExpTable& table, int* status, cudaStream_t stream) {
   switch (dtype) {
     case kDtypeFloat:
-      return launch_sample_t<float>(logits, rows, vocab, row_stride, inv_t, topp, rng_states,
-                                    out_ids, scratch, blocks, table, status, stream);
+      return launch_sample_t<float, false>(logits, rows, vocab, row_stride, inv_t, topp, rng_states,
+                                           out_ids, scratch, blocks, table, status, stream);
     case kDtypeHalf:
-      return launch_sample_t<__half>(logits, rows, vocab, row_stride, inv_t, topp, rng_states,
-                                     out_ids, scratch, blocks, table, status, stream);
-    case kDtypeBFloat16:
-      return launch_sample_t<__nv_bfloat16>(logits, rows, vocab, row_stride, inv_t, topp,
+      return launch_sample_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp,
                                             rng_states, out_ids, scratch, blocks, table, status,
                                             stream);
+    case kDtypeBFloat16:
+      return launch_sample_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp,
+                                                  rng_states, out_ids, scratch, blocks, table,
+                                                  status, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -767,13 +1036,13 @@ int sample_kernel_max_blocks_per_sm(int dtype) {
   cudaError_t e;
   switch (dtype) {
     case kDtypeFloat:
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float>, kThreads, 0);
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float, false>, kThreads, 0);
       break;
     case kDtypeHalf:
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half>, kThreads, 0);
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half, false>, kThreads, 0);
       break;
     default:
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16>, kThreads, 0);
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16, true>, kThreads, 0);
       break;
   }
   if (e != cudaSuccess || n < 1) n = 1;

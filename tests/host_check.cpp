@@ -26,11 +26,22 @@ bool tile(const float* v, int threads, int chunk, float& s, bool search, float t
       seq_identity(&mine[t]);
       if (t >= consumed) {
         if (kb >= 27 && !force_generic) {
+          // as the kernel: tie-free fast path first, two-parity redo of the chunk on a tie
           const float inv_u = seq_inv_u(kb);
-          for (int j = 0; j < chunk; ++j) seq_push_scaled(&mine[t], v[t * chunk + j], inv_u);
+          int acc = 0;
+          bool tie = false;
+          for (int j = 0; j < chunk; ++j) tie = seq_push_fast(&acc, v[t * chunk + j], inv_u) || tie;
+          if (acc > (1 << 25)) acc = 1 << 25;
+          mine[t].a0 = mine[t].a1 = acc;
+          if (tie) {
+            seq_identity(&mine[t]);
+            for (int j = 0; j < chunk; ++j) seq_push_scaled(&mine[t], v[t * chunk + j], inv_u);
+          }
         } else {
           for (int j = 0; j < chunk; ++j) seq_push(&mine[t], v[t * chunk + j], kb);
         }
+        if (mine[t].a0 > (1 << 25)) mine[t].a0 = 1 << 25;
+        if (mine[t].a1 > (1 << 25)) mine[t].a1 = 1 << 25;
       }
     }
     SeqSummary run;
@@ -109,7 +120,10 @@ float hc_seqsum(const float* v, long n, int threads, int chunk, int force_generi
   std::vector<float> buf(tile_elems);
   float s = 0.0f;
   long it = 0;
-  for (long base = 0; base < n; base += tile_elems) {
+  // the kernels add the first terms sequentially (head), then go tile by tile
+  const long head = force_generic == 2 ? 0 : (n < 256 ? n : 256);
+  for (long i = 0; i < head; ++i) s = s + v[i];
+  for (long base = head; base < n; base += tile_elems) {
     for (int i = 0; i < tile_elems; ++i) buf[i] = (base + i < n) ? v[base + i] : 0.0f;
     int hp;
     float hs;
