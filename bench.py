@@ -38,8 +38,8 @@ NBUF = 4  # rotating input buffers: 4 x 65.7 MB > 126 MB of L2
 FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes (read + write) of ONE launch of the sampling kernel on the benchmark batch, from
-# the ncu capture summarised in profiles/; None until a capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# the ncu capture summarised in profiles/sample_rows_kernel_bf16_c3_256rows.md.
+NCU_DRAM_BYTES_PER_LAUNCH = 71_690_000  # 67.61 MB read + 4.08 MB written
 
 
 def hbm_peak():
