@@ -37,6 +37,9 @@ SYMBOLS = {
                                                 C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "etb200_sampler_sample_rows_host": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
                                                      C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "etb200_sample_rows_static": (C.c_uint32, [C.c_int32, C.c_float, C.c_float, C.c_void_p, C.c_int32,
+                                               C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "etb200_static_last_error_message": (C.c_char_p, []),
     "etb200_selftest_expf": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "etb200_sampler_launch_count": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "etb200_last_error_message": (C.c_char_p, []),

@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libetb200_sampler.so")
 
-SOURCES = ["sampler_kernels.cu", "c_api.cu"]
+SOURCES = ["sampler_kernels.cu", "c_api.cu", "static_scratch.cu"]
 HEADERS = ["exact_math.cuh", "sampler_kernels.cuh", os.path.join("..", "..", "include", "etb200_sampler.h")]
 
 NVCC_FLAGS = [

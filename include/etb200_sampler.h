@@ -124,6 +124,32 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_host(
     etb200_sampler_t* handle, const void* logits_host, int32_t dtype, int64_t rows,
     int64_t row_stride_elems, uint64_t* rng_states_host, int64_t* out_ids_host, void* stream);
 
+/* No counterpart in the reference. For callers that may not allocate device memory: a
+ * runtime living inside a pre-planned arena, a tenant with a fixed memory budget on a
+ * shared GPU, a latency-critical loop that cannot take the implicit synchronisation of
+ * cudaMalloc/cudaFree.
+ * Same sampling as etb200_sampler_sample_rows (temperature, top-p / multinomial / argmax,
+ * per-row xorshift64* states advanced in place, int64 ids out) but without a handle and
+ * without any allocation: the kernel's candidate lists live in a fixed 64 MiB array inside
+ * the library image (every GPU that loads the library holds those 64 MiB until exit).
+ *   - Runs on the CURRENT CUDA device; enqueues on `stream`; does not synchronise.
+ *   - Limit: 16 * vocab_size bytes must fit the array, i.e. vocab_size <= 4194304; larger
+ *     sizes are refused with ETB200_INVALID_ARGUMENT. Fewer thread blocks run at once than
+ *     with a handle (32 at a 131072-entry vocabulary), so large batches are slower.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *   - All calls share the one array. Nothing in it has to start at zero (each call writes
+ *     its lists before reading them), and its contents after a call are meaningless. Two
+ *     calls whose kernels overlap on the same GPU (different streams, threads or
+ *     processes' contexts sharing the library image) race on it: serialise them.
+ *   - No top-k; rng_states_device is required whenever temperature != 0.
+ * Errors of this function are described by etb200_static_last_error_message(). */
+ETB200_EXPORT etb200_error_t etb200_sample_rows_static(
+    int32_t vocab_size, float temperature, float topp, const void* logits_device, int32_t dtype,
+    int64_t rows, int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* out_ids_device,
+    void* stream);
+ETB200_EXPORT const char* etb200_static_last_error_message(void);
+
 /* Diagnostic: y[i] = the library's device expf(x[i]) for n floats x <= 0 in device memory.
  * The sampler's results depend on expf matching the host libm that the reference calls
  * (sampler.cpp:201) bit for bit; this lets a test verify that on the machine at hand. */
