@@ -38,11 +38,21 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kChunk = 16;                  // consecutive logits per thread per tile
 constexpr int kTile = kThreads * kChunk;    // logits per tile
 constexpr int kHead = 256;                  // leading terms of a sum that one thread adds sequentially
-constexpr int kHistShift = 19;              // histogram bin = float bits >> 19 (exponent + 4 mantissa bits)
-constexpr int kHistBins = (0x3F800000 >> kHistShift) + 2;  // values in (0, 1]
+// Candidate values are binned by their float bits >> 21 (exponent + 2 mantissa bits). Bin
+// kBins-1 holds 1.0; bin 0 also collects everything below the covered range (e < ~2.4e-10).
+// Per bin two integers are kept: the count, and the sum of the 13 mantissa bits below the
+// bin bits, which together give the bin's mass to about 2^-15 relative (always rounded
+// down) without floating-point atomics.
+constexpr int kBinShift = 21;
+constexpr int kBins = 128;
+constexpr int kBinTop = 0x3F800000 >> kBinShift;  // bin index of 1.0 before rebasing
+constexpr int kBinBase = kBinTop - (kBins - 1);
 constexpr int kRadixBits = 8;
 constexpr int kRadix = 1 << kRadixBits;
 constexpr int kFastSat = 1 << 25;           // per-thread clamp of chunk summaries
+constexpr int kCompactSteps = 448;          // list entries compacted per segment = 448 * kThreads
+constexpr int kListBatch = 8;               // list entries a thread loads before using any of them
+constexpr int kRankSortMax = 256;           // survivor lists up to this size are rank-sorted in shared memory
 
 // bf16 table of e by logit bit pattern: both signs, |logit| in [2^-16, 2^8), plus +0 and -0.
 // Anything else (tiny, huge, infinite, NaN) is rare and computed directly.
@@ -58,27 +68,36 @@ struct Entry {
 
 template <bool kLut>
 struct __align__(16) Shared {
+  // (members read with vector loads carry their own alignas)
   static constexpr bool kHasLut = kLut;
   uint64_t exp_tab[kExpTableSize];
   float lut[kLut ? kLutSize : 2];
-  float head[kHead];
+  alignas(16) float head[kHead];  // read as float4
   SeqSummary wsum[kWarps];
-  int wsum_i[kWarps];
+  int wsum_i[2][kWarps];  // slots used by alternate scan rounds (see seqsum_tile)
+  int first[2];
+  int two_parity[2];
   int wcnt[2][kWarps];
   float redf[kWarps];
   int redi[kWarps];
+  unsigned hcnt[kBins];
+  float hmass[kBins];
   float s_bcast;
-  int first;
   int hit_found;
   int hit_idx;
   float hit_val;
   int misc_i[4];
   float misc_f[4];
   union {
+    unsigned wbins[kWarps][kBins][2];  // per warp and value bin: count, sum of mantissa offsets
     struct {
-      unsigned cnt[kHistBins];
-      float mass[kHistBins];
-    } hist;
+      unsigned short cnt[kCompactSteps][kWarps];  // survivors per (step, warp), then exclusive in step
+      unsigned base[kCompactSteps];               // survivors in front of each step
+    } compact;
+    struct {
+      unsigned long long ck[kRankSortMax];
+      int rank[kRankSortMax];
+    } rsort;
     struct {
       unsigned digit[kRadix];
       unsigned offs[kRadix];
@@ -136,7 +155,12 @@ __device__ __forceinline__ int block_excl_count(S& sm, int cnt, int* total) {
 // Each round summarises every thread's chunk in the binade of s. The common case has no
 // exact half-way tie anywhere in the tile: then a chunk's summary is one integer and the
 // block scan is a plain integer prefix sum. A tie anywhere switches the round to the
-// two-parity summaries of exact_math.cuh.
+// two-parity summaries of exact_math.cuh (one more barrier).
+//
+// Rounds alternate between two sets of shared slots (`rp`, block-uniform, carried by the
+// caller across tiles), so a round needs no barrier to protect its slots from the readers
+// of the previous round: two barriers per round, a third only when a chunk has to be
+// redone. Invariant at round entry: first[rp] == kThreads and two_parity[rp] == 0.
 //
 // With kSearch, also looks for the first term after which the running sum exceeds `thr`
 // (terms at position >= limit, counted from pos0 of thread 0's first term, must be zero
@@ -145,8 +169,8 @@ __device__ __forceinline__ int block_excl_count(S& sm, int cnt, int* total) {
 // ---------------------------------------------------------------------------------------
 template <bool kSearch, typename S>
 __device__ __forceinline__ bool seqsum_tile(
-    S& sm, const float (&v)[kChunk], float& s, float thr, int pos0, int limit, int* hit_pos,
-    float* hit_sum) {
+    S& sm, const float (&v)[kChunk], float& s, int& rp, float thr, int pos0, int limit,
+    int* hit_pos, float* hit_sum) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int consumed = 0;
   while (true) {
@@ -179,23 +203,18 @@ __device__ __forceinline__ bool seqsum_tile(
       if (mine.a0 > kFastSat) mine.a0 = kFastSat;
       if (mine.a1 > kFastSat) mine.a1 = kFastSat;
     }
-    // barrier: also separates this round from the previous readers of the shared slots
-    const int two_parity = __syncthreads_or(mine.a0 != mine.a1);
-    int n_in, n_out, n_total;
-    if (!two_parity) {
-      int inc = mine.a0;
+    if (mine.a0 != mine.a1) sm.two_parity[rp] = 1;
+    int inc = mine.a0;
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += o;
-      }
-      if (lane == 31) sm.wsum_i[warp] = inc < kFastSat ? inc : kFastSat;
-      if (tid == 0) {
-        sm.first = kThreads;
-        sm.hit_found = 0;
-      }
-      __syncthreads();
-      int wt = (lane < kWarps) ? sm.wsum_i[lane] : 0;
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += o;
+    }
+    if (lane == 31) sm.wsum_i[rp][warp] = inc < kFastSat ? inc : kFastSat;
+    __syncthreads();  // ---- barrier 1
+    int n_in, n_out, n_total;
+    if (!sm.two_parity[rp]) {
+      int wt = (lane < kWarps) ? sm.wsum_i[rp][lane] : 0;
 #pragma unroll
       for (int d = 1; d < kWarps; d <<= 1) {
         const int o = __shfl_up_sync(0xffffffffu, wt, d);
@@ -207,24 +226,20 @@ __device__ __forceinline__ bool seqsum_tile(
       n_in = n_s + pre + (inc - mine.a0);
       n_out = n_in + mine.a0;
     } else {
-      SeqSummary inc = mine;
+      SeqSummary sc = mine;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         SeqSummary o;
-        o.a0 = __shfl_up_sync(0xffffffffu, inc.a0, d);
-        o.a1 = __shfl_up_sync(0xffffffffu, inc.a1, d);
-        if (lane >= d) inc = seq_compose(o, inc);
+        o.a0 = __shfl_up_sync(0xffffffffu, sc.a0, d);
+        o.a1 = __shfl_up_sync(0xffffffffu, sc.a1, d);
+        if (lane >= d) sc = seq_compose(o, sc);
       }
       SeqSummary excl;
-      excl.a0 = __shfl_up_sync(0xffffffffu, inc.a0, 1);
-      excl.a1 = __shfl_up_sync(0xffffffffu, inc.a1, 1);
+      excl.a0 = __shfl_up_sync(0xffffffffu, sc.a0, 1);
+      excl.a1 = __shfl_up_sync(0xffffffffu, sc.a1, 1);
       if (lane == 0) seq_identity(&excl);
-      if (lane == 31) sm.wsum[warp] = inc;
-      if (tid == 0) {
-        sm.first = kThreads;
-        sm.hit_found = 0;
-      }
-      __syncthreads();
+      if (lane == 31) sm.wsum[warp] = sc;
+      __syncthreads();  // ---- extra barrier of a two-parity round
       // every warp redundantly scans the kWarps warp totals with shuffles
       SeqSummary wt;
       seq_identity(&wt);
@@ -252,9 +267,16 @@ __device__ __forceinline__ bool seqsum_tile(
       if (active && n_out < kSeqLimit && seq_value(kb, n_out) > thr) flag = true;
     }
     const unsigned ballot = __ballot_sync(0xffffffffu, flag);
-    if (ballot != 0 && lane == 0) atomicMin(&sm.first, warp * 32 + __ffs(ballot) - 1);
-    __syncthreads();
-    const int first = sm.first;
+    if (ballot != 0 && lane == 0) atomicMin(&sm.first[rp], warp * 32 + __ffs(ballot) - 1);
+    if (tid == 0) {
+      // prepare the other slot set for the next round; its last readers are behind barrier 1
+      sm.first[rp ^ 1] = kThreads;
+      sm.two_parity[rp ^ 1] = 0;
+      sm.hit_found = 0;
+    }
+    __syncthreads();  // ---- barrier 2
+    const int first = sm.first[rp];
+    rp ^= 1;
     if (first == kThreads) {
       // nothing left the binade: the whole tile is summarised exactly
       s = seq_value(kb, n_total);
@@ -280,7 +302,7 @@ __device__ __forceinline__ bool seqsum_tile(
       }
       sm.s_bcast = acc;
     }
-    __syncthreads();
+    __syncthreads();  // ---- barrier 3 (only in rounds that redo a chunk)
     s = sm.s_bcast;
     if (kSearch && sm.hit_found) {
       *hit_pos = sm.hit_idx;
@@ -301,16 +323,32 @@ __device__ __forceinline__ bool head_sum(
     S& sm, int count, float& s, float thr, int pos0, int* hit_pos, float* hit_sum) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    // sm.head is zero-padded to a multiple of 4, and the terms are non-negative, so the
+    // partial sums only grow: test four additions at a time
     float acc = s;
     int found = 0;
-    for (int i = 0; i < count; ++i) {
-      acc = __fadd_rn(acc, sm.head[i]);
-      if (kSearch && acc > thr) {
-        found = 1;
-        sm.hit_idx = pos0 + i;
-        sm.hit_val = acc;
+    const float4* h4 = reinterpret_cast<const float4*>(sm.head);
+    for (int i = 0; i < count; i += 4) {
+      const float4 q = h4[i >> 2];
+      const float a1 = __fadd_rn(acc, q.x);
+      const float a2 = __fadd_rn(a1, q.y);
+      const float a3 = __fadd_rn(a2, q.z);
+      const float a4 = __fadd_rn(a3, q.w);
+      if (kSearch && a4 > thr) {
+        int k = 3;
+        float hv = a4;
+        if (a3 > thr) { k = 2; hv = a3; }
+        if (a2 > thr) { k = 1; hv = a2; }
+        if (a1 > thr) { k = 0; hv = a1; }
+        if (i + k < count) {
+          found = 1;
+          sm.hit_idx = pos0 + i + k;
+          sm.hit_val = hv;
+        }
+        acc = a4;
         break;
       }
+      acc = a4;
     }
     sm.hit_found = found;
     sm.s_bcast = acc;
@@ -359,12 +397,13 @@ struct RowMath {
 
   // bf16 bit pattern -> table slot, or -1 when the value is outside the table
   static __device__ __forceinline__ int lut_slot(uint32_t h) {
+    // selects only: sixteen of these run back to back and must not split the warp
     const uint32_t a = h & 0x7FFFu;
     const uint32_t sgn = h >> 15;
     const uint32_t k = a - (uint32_t)(kLutExpLo << 7);
-    if (k < (uint32_t)kLutPerSign) return (int)(k + sgn * kLutPerSign);
-    if (a == 0) return 2 * kLutPerSign + (int)sgn;
-    return -1;
+    const int in_table = (int)(k + sgn * kLutPerSign);
+    const int zero = 2 * kLutPerSign + (int)sgn;
+    return k < (uint32_t)kLutPerSign ? in_table : (a == 0 ? zero : -1);
   }
 
   static __device__ __forceinline__ uint32_t lut_pattern(int slot) {
@@ -394,6 +433,55 @@ struct RowMath {
       return from_pattern((uint32_t) reinterpret_cast<const unsigned short*>(row)[i], sm);
     } else {
       return direct(to_f32(row[i]), sm);
+    }
+  }
+
+  // The 128-bit loads of a full, aligned chunk, separated from their use so that the next
+  // tile's loads can be in flight while this tile is processed.
+  static constexpr int kRawVecs = kChunk * sizeof(T) / 16;
+  struct Raw {
+    uint4 q[kRawVecs];
+  };
+  __device__ __forceinline__ bool full(int i0) const { return vec_ok && i0 + kChunk <= vocab; }
+  __device__ __forceinline__ void load_raw(int i0, Raw* r) const {
+#pragma unroll
+    for (int q = 0; q < kRawVecs; ++q) r->q[q] = __ldg(reinterpret_cast<const uint4*>(row + i0) + q);
+  }
+  __device__ __forceinline__ void eval_raw(const Raw& r, const S& sm, float (&e)[kChunk]) const {
+    constexpr int kPerVec = 16 / sizeof(T);
+    int outside = 0;
+    (void)outside;
+#pragma unroll
+    for (int q = 0; q < kRawVecs; ++q) {
+      if constexpr (S::kHasLut) {
+        const uint32_t w[4] = {r.q[q].x, r.q[q].y, r.q[q].z, r.q[q].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int s0 = lut_slot(w[j] & 0xFFFFu);
+          const int s1 = lut_slot(w[j] >> 16);
+          outside |= (s0 | s1);  // sign bit set if any pattern is outside the table
+          e[q * 8 + 2 * j] = sm.lut[s0 < 0 ? 0 : s0];
+          e[q * 8 + 2 * j + 1] = sm.lut[s1 < 0 ? 0 : s1];
+        }
+      } else {
+        const T* p = reinterpret_cast<const T*>(&r.q[q]);
+#pragma unroll
+        for (int j = 0; j < kPerVec; ++j) e[q * kPerVec + j] = direct(to_f32(p[j]), sm);
+      }
+    }
+    if constexpr (S::kHasLut) {
+      if (outside < 0) {
+        // rare: a tiny, huge or non-finite logit in this chunk; redo those elements directly
+#pragma unroll
+        for (int q = 0; q < kRawVecs; ++q) {
+          const uint32_t w[4] = {r.q[q].x, r.q[q].y, r.q[q].z, r.q[q].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (lut_slot(w[j] & 0xFFFFu) < 0) e[q * 8 + 2 * j] = direct(bits_f32((w[j] & 0xFFFFu) << 16), sm);
+            if (lut_slot(w[j] >> 16) < 0) e[q * 8 + 2 * j + 1] = direct(bits_f32(w[j] & 0xFFFF0000u), sm);
+          }
+        }
+      }
     }
   }
 
@@ -535,7 +623,8 @@ __device__ void radix_pass_desc(S& sm, const Entry* src, Entry* dst, int n, int 
 // buffer; long ones continue with block-wide tiles.
 template <typename S>
 __device__ bool list_search(
-    S& sm, const Entry* list, int n, int limit, float thr, int* pos, float* sum, float* total) {
+    S& sm, const Entry* list, int n, int limit, float thr, int& rp, int* pos, float* sum,
+    float* total) {
   const int lim = n < limit ? n : limit;
   float s = 0.0f;
   const int seq_end = lim <= 4 * kHead ? lim : kHead;
@@ -556,7 +645,7 @@ __device__ bool list_search(
       const int i = base + threadIdx.x * kChunk + j;
       v[j] = (i < lim) ? bits_f32(list[i].key) : 0.0f;
     }
-    if (seqsum_tile<true>(sm, v, s, thr, base, lim, pos, sum)) return true;
+    if (seqsum_tile<true>(sm, v, s, rp, thr, base, lim, pos, sum)) return true;
   }
   *total = s;
   return false;
@@ -576,6 +665,11 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   __shared__ S sm;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
+  if (tid < 2) {
+    sm.first[tid] = kThreads;
+    sm.two_parity[tid] = 0;
+  }
+  int rp = 0;  // which set of scan-round slots the next round uses (see seqsum_tile)
   __syncthreads();
   const bool use_topp = !(topp <= 0.0f || topp >= 1.0f);
   Entry* listA = scratch + (size_t)blockIdx.x * 2 * (size_t)vocab;
@@ -612,41 +706,71 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     float s = 0.0f;
     int n_a = 0;
     {
-      // head: the first kHead terms, added by one thread
+      // head: the first kHead terms are added by one thread (a sum changes binade every few
+      // additions at its start); their candidates are listed by all threads meanwhile
       __syncthreads();  // the table is complete
       const int cnt = vocab < kHead ? vocab : kHead;
-      if (tid < kHead) sm.head[tid] = rm.at(tid, sm);
+      float e_mine = 0.0f;
+      if (tid < kHead) {
+        e_mine = rm.at(tid, sm);
+        sm.head[tid] = e_mine;
+      }
+      const bool cand = use_topp && tid < cnt && e_mine >= e_floor;
+      const unsigned cb = __ballot_sync(0xffffffffu, cand);
+      if (lane == 0) sm.wcnt[0][warp] = __popc(cb);
       __syncthreads();
       if (tid == 0) {
         float acc = 0.0f;
-        int n = 0;
-        for (int i = 0; i < cnt; ++i) {
-          const float e = sm.head[i];
-          acc = __fadd_rn(acc, e);
-          if (use_topp && e >= e_floor) {
-            Entry en;
-            en.key = f32_bits(e);
-            en.idx = i;
-            listA[n++] = en;
-          }
+        const float4* h4 = reinterpret_cast<const float4*>(sm.head);
+        for (int i = 0; i < cnt; i += 4) {
+          const float4 q = h4[i >> 2];  // zero beyond the row
+          acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, q.x), q.y), q.z), q.w);
         }
         sm.s_bcast = acc;
-        sm.misc_i[0] = n;
+      }
+      int pre = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const int c = sm.wcnt[0][w];
+        if (w < warp) pre += c;
+        n_a += c;
+      }
+      if (cand) {
+        Entry en;
+        en.key = f32_bits(e_mine);
+        en.idx = tid;
+        listA[pre + __popc(cb & ((1u << lane) - 1u))] = en;
       }
       __syncthreads();
       s = sm.s_bcast;
-      n_a = sm.misc_i[0];
     }
     int buf = 0;
+    constexpr bool kPrefetch = sizeof(T) == 2;  // 8 registers; fp32 chunks would need 16
+    typename RowMath<T, S>::Raw raw_next;
+    if (kPrefetch && kHead < vocab && rm.full(kHead + tid * kChunk)) rm.load_raw(kHead + tid * kChunk, &raw_next);
     for (int base = kHead; base < vocab; base += kTile) {
       const int i0 = base + tid * kChunk;
       float e[kChunk];
-      rm.chunk(i0, sm, e);
+      if (kPrefetch) {
+        if (rm.full(i0)) {
+          const typename RowMath<T, S>::Raw raw = raw_next;
+          const int inext = i0 + kTile;
+          if (inext < vocab && rm.full(inext)) rm.load_raw(inext, &raw_next);
+          rm.eval_raw(raw, sm, e);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) e[j] = rm.at(i0 + j, sm);
+        }
+      } else {
+        rm.chunk(i0, sm, e);
+      }
+      // p_i >= cutoff needs e_i >= cutoff * S, and S is at least the running sum so far
+      const float floor_now = use_topp ? fmaxf(e_floor, cutoff * s * 0.999999f) : 0.0f;
       int cnt = 0, inc = 0;
       if (use_topp) {
-        // entries beyond the row are 0 and e_floor > 0, so they never count
+        // entries beyond the row are 0 and the floor is > 0, so they never count
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) cnt += (e[j] >= e_floor) ? 1 : 0;
+        for (int j = 0; j < kChunk; ++j) cnt += (e[j] >= floor_now) ? 1 : 0;
         inc = cnt;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -657,7 +781,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       }
       int hp;
       float hs;
-      seqsum_tile<false>(sm, e, s, 0.0f, base, vocab, &hp, &hs);
+      seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
       if (use_topp) {
         int pre = 0, tot = 0;
 #pragma unroll
@@ -670,7 +794,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         if (cnt > 0) {
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
-            if (e[j] >= e_floor) {
+            if (e[j] >= floor_now) {
               Entry en;
               en.key = f32_bits(e[j]);
               en.idx = i0 + j;
@@ -705,39 +829,66 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       for (int base = kHead; base < vocab && !hit; base += kTile) {
         float p[kChunk];
         rm.chunk(base + tid * kChunk, sm, p);
-        hit = seqsum_tile<true>(sm, p, cdf, coin, base, vocab, &hp, &hs);
+        hit = seqsum_tile<true>(sm, p, cdf, rp, coin, base, vocab, &hp, &hs);
       }
       if (hit) token = hp;
     } else {
       // ---- pass 3b: sample_topp (sampler.cpp:122-171)
       __threadfence_block();
       __syncthreads();
-      // histogram of the listed e values: counts and approximate mass per bin
-      for (int b = tid; b < kHistBins; b += kThreads) {
-        sm.u.hist.cnt[b] = 0;
-        sm.u.hist.mass[b] = 0.0f;
+      // value bins of the listed candidates: per-warp integer counters, filled by one
+      // coalesced pass over the list (every lane busy, unlike binning inside pass 2)
+      for (int b = tid; b < kWarps * kBins * 2; b += kThreads) (&sm.u.wbins[0][0][0])[b] = 0;
+      __syncthreads();
+      for (int i0 = 0; i0 < n_a; i0 += kListBatch * kThreads) {
+        uint32_t k[kListBatch];
+#pragma unroll
+        for (int u = 0; u < kListBatch; ++u) {  // independent loads first, so they overlap
+          const int i = i0 + u * kThreads + tid;
+          k[u] = i < n_a ? listA[i].key : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < kListBatch; ++u) {
+          if (i0 + u * kThreads + tid < n_a) {
+            int bin = (int)(k[u] >> kBinShift) - kBinBase;
+            bin = bin < 0 ? 0 : (bin < kBins ? bin : kBins - 1);
+            atomicAdd(&sm.u.wbins[warp][bin][0], 1u);
+            atomicAdd(&sm.u.wbins[warp][bin][1], (k[u] >> 8) & 0x1FFFu);
+          }
+        }
       }
       __syncthreads();
-      for (int i = tid; i < n_a; i += kThreads) {
-        const uint32_t k = listA[i].key;
-        int b = (int)(k >> kHistShift);
-        b = b < kHistBins ? b : kHistBins - 1;
-        atomicAdd(&sm.u.hist.cnt[b], 1u);
-        atomicAdd(&sm.u.hist.mass[b], bits_f32(k));
+      // Per-bin counts of the listed values and the mass they hold, slightly rounded down: a
+      // value whose bits are (bin << 21 | off) equals edge(bin) + off * 2^(exponent - 23), and
+      // off was accumulated with its top 13 bits only. Bin 0 also holds everything below the
+      // covered range, so its mass counts as 0.
+      if (tid < kBins) {
+        unsigned c = 0, o = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          c += sm.u.wbins[w][tid][0];
+          o += sm.u.wbins[w][tid][1];
+        }
+        const uint32_t edge_bits = (uint32_t)(tid + kBinBase) << kBinShift;
+        const float edge = bits_f32(edge_bits);
+        // one unit of the 13-bit offset is 2^8 units of the last place of the bin's binade
+        const float unit = bits_f32(edge_bits & 0x7F800000u) * (256.0f / 8388608.0f);
+        sm.hcnt[tid] = c;
+        sm.hmass[tid] = tid == 0 ? 0.0f : (float)c * edge + (float)o * unit;
       }
       __syncthreads();
-      // Lowest bin to keep: the largest b whose bins >= b hold clearly more than topp of the
-      // mass. The margin covers the rounding of the approximate masses and of the reference's
-      // own running sum; the choice only has to be safe, not tight, and is verified below.
+      // Lowest bin to keep: the largest b whose bins >= b surely hold more than topp of the
+      // mass. The margin covers the rounding of the reference's own running sum; the choice
+      // only has to be safe, not tight, and is verified below.
       if (tid < 32) {
         float acc = 0.0f;
         unsigned cacc = 0;
         int chosen = 0, chosen_cnt = 0;
         bool done = false;
-        for (int hi = kHistBins - 1; hi >= 0 && !done; hi -= 32) {
+        for (int hi = kBins - 1; hi >= 0 && !done; hi -= 32) {
           const int b = hi - tid;
-          float m = (b >= 0) ? sm.u.hist.mass[b] : 0.0f;
-          unsigned c = (b >= 0) ? sm.u.hist.cnt[b] : 0u;
+          float m = (b >= 0) ? sm.hmass[b] : 0.0f;
+          unsigned c = (b >= 0) ? sm.hcnt[b] : 0u;
 #pragma unroll
           for (int d = 1; d < 32; d <<= 1) {
             const float om = __shfl_up_sync(0xffffffffu, m, d);
@@ -777,33 +928,75 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       for (int attempt = 0; attempt < 2 && !have; ++attempt) {
         // compact list A -> list B: survivors of the value threshold that pass the cutoff
         // crop, with their probabilities, still in index order
+        const uint32_t key_lo = bin_lo > 0 ? (uint32_t)(bin_lo + kBinBase) << kBinShift : 0u;
+        // Two coalesced passes over list A per segment of kCompactSteps * kThreads entries:
+        // count the survivors of every (step, warp), prefix those counts, then write the
+        // survivors in list order.
         n_b = 0;
-        const uint32_t key_lo = (uint32_t)bin_lo << kHistShift;
-        constexpr int kPer = 8;
-        for (int base = 0; base < n_a; base += kThreads * kPer) {
-          Entry en[kPer];
-          unsigned keep = 0;
+        for (int seg0 = 0; seg0 < n_a; seg0 += kCompactSteps * kThreads) {
+          const int seg_n = (n_a - seg0) < kCompactSteps * kThreads ? (n_a - seg0) : kCompactSteps * kThreads;
+          const int steps = (seg_n + kThreads - 1) / kThreads;
+          __syncthreads();  // earlier users of the union are done
+          for (int st0 = 0; st0 < steps; st0 += kListBatch) {
+            uint32_t k[kListBatch];
 #pragma unroll
-          for (int j = 0; j < kPer; ++j) {
-            const int i = base + tid * kPer + j;
-            en[j].key = 0;
-            en[j].idx = 0;
-            if (i < n_a) {
-              en[j] = listA[i];
-              if (en[j].key >= key_lo) {
-                const float p = __fdiv_rn(bits_f32(en[j].key), sum);
-                if (p >= cutoff) keep |= 1u << j;
-                en[j].key = f32_bits(p);
+            for (int u = 0; u < kListBatch; ++u) {
+              const int i = seg0 + (st0 + u) * kThreads + tid;
+              k[u] = (st0 + u < steps && i < n_a) ? listA[i].key : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < kListBatch; ++u) {
+              if (st0 + u < steps) {  // block-uniform
+                const int i = seg0 + (st0 + u) * kThreads + tid;
+                const bool keep = i < n_a && k[u] >= key_lo && __fdiv_rn(bits_f32(k[u]), sum) >= cutoff;
+                const unsigned kbal = __ballot_sync(0xffffffffu, keep);
+                if (lane == 0) sm.u.compact.cnt[st0 + u][warp] = (unsigned short)__popc(kbal);
               }
             }
           }
-          int tot;
-          int off = n_b + block_excl_count(sm, __popc(keep), &tot);
+          __syncthreads();
+          // thread t owns step t: exclusive prefix inside the step, and the step total
+          int step_total = 0;
+          if (tid < steps) {
 #pragma unroll
-          for (int j = 0; j < kPer; ++j) {
-            if (keep & (1u << j)) listB[off++] = en[j];
+            for (int w = 0; w < kWarps; ++w) {
+              const int c = sm.u.compact.cnt[tid][w];
+              sm.u.compact.cnt[tid][w] = (unsigned short)step_total;
+              step_total += c;
+            }
           }
-          n_b += tot;
+          int seg_total;
+          const int step_base = block_excl_count(sm, step_total, &seg_total);
+          if (tid < steps) sm.u.compact.base[tid] = (unsigned)(n_b + step_base);
+          __syncthreads();
+          for (int st0 = 0; st0 < steps; st0 += kListBatch) {
+            Entry en[kListBatch];
+#pragma unroll
+            for (int u = 0; u < kListBatch; ++u) {
+              const int i = seg0 + (st0 + u) * kThreads + tid;
+              en[u].key = 0;
+              en[u].idx = 0;
+              if (st0 + u < steps && i < n_a) en[u] = listA[i];
+            }
+#pragma unroll
+            for (int u = 0; u < kListBatch; ++u) {
+              if (st0 + u < steps) {  // block-uniform
+                const int i = seg0 + (st0 + u) * kThreads + tid;
+                bool keep = false;
+                if (i < n_a && en[u].key >= key_lo) {
+                  const float p = __fdiv_rn(bits_f32(en[u].key), sum);
+                  keep = p >= cutoff;
+                  en[u].key = f32_bits(p);
+                }
+                const unsigned kbal = __ballot_sync(0xffffffffu, keep);
+                if (keep) {
+                  listB[sm.u.compact.base[st0 + u] + sm.u.compact.cnt[st0 + u][warp] +
+                        __popc(kbal & ((1u << lane) - 1u))] = en[u];
+                }
+              }
+            }
+          }
+          n_b += seg_total;
         }
         __threadfence_block();
         __syncthreads();
@@ -811,19 +1004,48 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         // ping-pong between list B and free scratch (the tail of list A's buffer, or list A
         // itself once it is no longer needed); after an even number of passes the result is
         // back in list B.
-        Entry* ping = listB;
-        Entry* pong = (n_a + n_b <= vocab) ? listA + n_a : listA;
-        for (int pass = 0; pass < 32 / kRadixBits; ++pass) {
-          radix_pass_desc(sm, ping, pong, n_b, pass * kRadixBits);
+        if (n_b <= kRankSortMax) {
+          // small survivor set: rank every entry against all others. Composite key =
+          // (probability bits, inverted index): larger means earlier in the sorted order.
+          // Two threads share an entry, each scanning half of the list.
+          const int ent = tid & (kRankSortMax - 1), part = tid / kRankSortMax;
+          Entry en;
+          en.key = 0;
+          en.idx = 0;
+          if (tid < n_b) {
+            en = listB[tid];
+            sm.u.rsort.ck[tid] = ((unsigned long long)en.key << 32) | (uint32_t)(0x7FFFFFFF - en.idx);
+            sm.u.rsort.rank[tid] = 0;
+          }
+          __syncthreads();
+          if (ent < n_b) {
+            const unsigned long long mine = sm.u.rsort.ck[ent];
+            constexpr int kParts = kThreads / kRankSortMax;
+            const int per = (n_b + kParts - 1) / kParts;
+            const int j0 = part * per, j1 = (j0 + per) < n_b ? (j0 + per) : n_b;
+            int rank = 0;
+#pragma unroll 8
+            for (int j = j0; j < j1; ++j) rank += sm.u.rsort.ck[j] > mine ? 1 : 0;
+            atomicAdd(&sm.u.rsort.rank[ent], rank);
+          }
+          __syncthreads();
+          if (tid < n_b) listB[sm.u.rsort.rank[tid]] = en;
           __threadfence_block();
-          Entry* t = ping;
-          ping = pong;
-          pong = t;
+        } else {
+          Entry* ping = listB;
+          Entry* pong = (n_a + n_b <= vocab) ? listA + n_a : listA;
+          for (int pass = 0; pass < 32 / kRadixBits; ++pass) {
+            radix_pass_desc(sm, ping, pong, n_b, pass * kRadixBits);
+            __threadfence_block();
+            Entry* t = ping;
+            ping = pong;
+            pong = t;
+          }
         }
         __syncthreads();
         int pos;
         float hs, total;
-        if (list_search(sm, listB, n_b, n_b, topp, &pos, &hs, &total)) {
+        if (list_search(sm, listB, n_b, n_b, topp, rp, &pos, &hs, &total)) {
           have = true;
           last_idx = pos;
           cum = hs;
@@ -844,7 +1066,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         int pos;
         float hs, total;
         int j = last_idx;
-        if (list_search(sm, listB, n_b, last_idx + 1, rr, &pos, &hs, &total)) j = pos;
+        if (list_search(sm, listB, n_b, last_idx + 1, rr, rp, &pos, &hs, &total)) j = pos;
         token = listB[j].idx;
       }
     }
