@@ -52,7 +52,7 @@ constexpr int kRadix = 1 << kRadixBits;
 constexpr int kFastSat = 1 << 25;           // per-thread clamp of chunk summaries
 constexpr int kCompactSteps = 448;          // list entries compacted per segment = 448 * kThreads
 constexpr int kListBatch = 8;               // list entries a thread loads before using any of them
-constexpr int kRankSortMax = 256;           // survivor lists up to this size are rank-sorted in shared memory
+constexpr int kRankSortMax = 512;           // survivor lists up to this size are rank-sorted in shared memory
 
 // bf16 table of e by logit bit pattern: both signs, |logit| in [2^-16, 2^8), plus +0 and -0.
 // Anything else (tiny, huge, infinite, NaN) is rare and computed directly.
@@ -1007,7 +1007,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         if (n_b <= kRankSortMax) {
           // small survivor set: rank every entry against all others. Composite key =
           // (probability bits, inverted index): larger means earlier in the sorted order.
-          // Two threads share an entry, each scanning half of the list.
+          // kThreads / kRankSortMax threads share an entry, each scanning a part of the list.
           const int ent = tid & (kRankSortMax - 1), part = tid / kRankSortMax;
           Entry en;
           en.key = 0;
