@@ -185,22 +185,21 @@ etb200_error_t sample_rows_device(
     return fail(ETB200_NOT_SUPPORTED,
                 "UInt16 logits are raw integers: only temperature 0 (argmax) is meaningful for them");
   }
-  if (h->topk > 0 && h->topk < h->vocab) {
-    return fail(ETB200_NOT_SUPPORTED, "top-k sampling (set_topk(%d)) is not built yet", h->topk);
-  }
   if (rng_states == nullptr) {
     ETB_CHECK_ARG(rows == 1, "rng_states may be NULL only for a single row (rows = %lld)", (long long)rows);
     rng_states = h->d_state;
   }
+  // top-k when 0 < k < vocab, and then top-p is ignored (sampler.cpp:239-241)
+  const int topk = (h->topk > 0 && h->topk < h->vocab) ? h->topk : 0;
   const bool use_topp = !(h->topp <= 0.0f || h->topp >= 1.0f);
   const int blocks = grid_blocks(h, dtype, rows);
-  if (use_topp) {
+  if (use_topp || topk > 0) {
     etb200_error_t err = ensure_scratch(h, blocks);
     if (err != ETB200_OK) return err;
   }
   ETB_CUDA(launch_sample_rows(
-      dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, rng_states, out_ids,
-      h->scratch, blocks, h->table, h->d_status, stream));
+      dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk, rng_states,
+      out_ids, h->scratch, blocks, h->table, h->d_status, stream));
   h->launches += 1;
   return ETB200_OK;
 }

@@ -658,8 +658,8 @@ __device__ bool list_search(
 template <typename T, bool kLut>
 __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
-    float topp, unsigned long long* __restrict__ rng_states, int64_t* __restrict__ out_ids,
-    Entry* scratch, ExpTable table, int* __restrict__ status) {
+    float topp, int topk, unsigned long long* __restrict__ rng_states,
+    int64_t* __restrict__ out_ids, Entry* scratch, ExpTable table, int* __restrict__ status) {
   (void)status;
   using S = Shared<kLut>;
   __shared__ S sm;
@@ -671,7 +671,10 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   }
   int rp = 0;  // which set of scan-round slots the next round uses (see seqsum_tile)
   __syncthreads();
-  const bool use_topp = !(topp <= 0.0f || topp >= 1.0f);
+  // mode selection of Sampler::sample (sampler.cpp:239-248): top-k wins over top-p
+  const bool use_topk = topk > 0 && topk < vocab;
+  const bool use_topp = !use_topk && !(topp <= 0.0f || topp >= 1.0f);
+  const bool use_list = use_topk || use_topp;  // modes that collect candidates during pass 2
   Entry* listA = scratch + (size_t)blockIdx.x * 2 * (size_t)vocab;
   Entry* listB = listA + vocab;
 
@@ -702,7 +705,8 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     // sampler.cpp:136-143: p_i >= cutoff needs e_i >= cutoff * S and S >= 1 (the maximum
     // contributes exactly 1), so e_i >= cutoff * (1 - 1e-6) is necessary.
     const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
-    const float e_floor = use_topp ? cutoff * 0.999999f : 0.0f;
+    // Top-k has no crop: it lists every entry with e > 0 (the smallest positive float as floor).
+    const float e_floor = use_topp ? cutoff * 0.999999f : (use_topk ? 1.4e-45f : 0.0f);
     float s = 0.0f;
     int n_a = 0;
     {
@@ -715,7 +719,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         e_mine = rm.at(tid, sm);
         sm.head[tid] = e_mine;
       }
-      const bool cand = use_topp && tid < cnt && e_mine >= e_floor;
+      const bool cand = use_list && tid < cnt && e_mine >= e_floor;
       const unsigned cb = __ballot_sync(0xffffffffu, cand);
       if (lane == 0) sm.wcnt[0][warp] = __popc(cb);
       __syncthreads();
@@ -765,9 +769,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         rm.chunk(i0, sm, e);
       }
       // p_i >= cutoff needs e_i >= cutoff * S, and S is at least the running sum so far
-      const float floor_now = use_topp ? fmaxf(e_floor, cutoff * s * 0.999999f) : 0.0f;
+      const float floor_now = use_topp ? fmaxf(e_floor, cutoff * s * 0.999999f) : e_floor;
       int cnt = 0, inc = 0;
-      if (use_topp) {
+      if (use_list) {
         // entries beyond the row are 0 and the floor is > 0, so they never count
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) cnt += (e[j] >= floor_now) ? 1 : 0;
@@ -782,7 +786,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       int hp;
       float hs;
       seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
-      if (use_topp) {
+      if (use_list) {
         int pre = 0, tot = 0;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
@@ -811,7 +815,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const float coin = sm.misc_f[0];
     int token;
 
-    if (!use_topp) {
+    if (!use_list) {
       // ---- pass 3a: sample_mult (sampler.cpp:58-70): running float cdf of p_i = e_i / S
       token = vocab - 1;
       rm.sum = sum;
@@ -833,7 +837,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       }
       if (hit) token = hp;
     } else {
-      // ---- pass 3b: sample_topp (sampler.cpp:122-171)
+      // ---- pass 3b: sample_topp (sampler.cpp:122-171) or sample_topk (sampler.cpp:72-120)
       __threadfence_block();
       __syncthreads();
       // value bins of the listed candidates: per-warp integer counters, filled by one
@@ -901,7 +905,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
           const float mass_above = acc + m;
           const float cnt_above = (float)(cacc + c);
           const float need = sum * (topp * 1.002f + 0.001f + cnt_above * 4.8e-7f);
-          const unsigned ok = __ballot_sync(0xffffffffu, b >= 0 && mass_above >= need);
+          // top-p: enough mass above; top-k: at least k entries above (bin 0 is unbounded below)
+          const bool enough = use_topk ? (b > 0 && cacc + c >= (unsigned)topk) : (mass_above >= need);
+          const unsigned ok = __ballot_sync(0xffffffffu, b >= 0 && enough);
           if (ok) {
             const int sel = __ffs(ok) - 1;
             chosen = hi - sel;
@@ -914,8 +920,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         if (tid == 0) {
           // The sort below ping-pongs into the free space behind list A, which must hold the
           // survivors; if it cannot, take the complete candidate set (then list A may be
-          // overwritten because no second attempt is ever needed).
-          if (!done || n_a + chosen_cnt > vocab) chosen = 0;
+          // overwritten because no second attempt is ever needed). Top-k never needs a second
+          // attempt: its threshold is an exact count.
+          if (!done || (!use_topk && n_a + chosen_cnt > vocab)) chosen = 0;
           sm.misc_i[1] = chosen;
         }
       }
@@ -948,7 +955,8 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
             for (int u = 0; u < kListBatch; ++u) {
               if (st0 + u < steps) {  // block-uniform
                 const int i = seg0 + (st0 + u) * kThreads + tid;
-                const bool keep = i < n_a && k[u] >= key_lo && __fdiv_rn(bits_f32(k[u]), sum) >= cutoff;
+                const bool keep = i < n_a && k[u] >= key_lo &&
+                                  (use_topk || __fdiv_rn(bits_f32(k[u]), sum) >= cutoff);
                 const unsigned kbal = __ballot_sync(0xffffffffu, keep);
                 if (lane == 0) sm.u.compact.cnt[st0 + u][warp] = (unsigned short)__popc(kbal);
               }
@@ -985,7 +993,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
                 bool keep = false;
                 if (i < n_a && en[u].key >= key_lo) {
                   const float p = __fdiv_rn(bits_f32(en[u].key), sum);
-                  keep = p >= cutoff;
+                  keep = use_topk || p >= cutoff;
                   en[u].key = f32_bits(p);
                 }
                 const unsigned kbal = __ballot_sync(0xffffffffu, keep);
@@ -1045,7 +1053,15 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         __syncthreads();
         int pos;
         float hs, total;
-        if (list_search(sm, listB, n_b, n_b, topp, rp, &pos, &hs, &total)) {
+        if (use_topk) {
+          // the k most probable entries (fewer if fewer have e > 0); their float sum in
+          // sorted order is topk_sum (sampler.cpp:105-108)
+          const int kk = topk < n_b ? topk : n_b;
+          list_search(sm, listB, n_b, kk, INFINITY, rp, &pos, &hs, &total);
+          have = true;
+          last_idx = kk - 1;
+          cum = total;
+        } else if (list_search(sm, listB, n_b, n_b, topp, rp, &pos, &hs, &total)) {
           have = true;
           last_idx = pos;
           cum = hs;
@@ -1198,28 +1214,28 @@ int sampler_threads() { return kThreads; }
 template <typename T, bool kLut>
 static cudaError_t launch_sample_t(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
-    unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
+    int topk, unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
     const ExpTable& table, int* status, cudaStream_t stream) {
   sample_rows_kernel<T, kLut><<<blocks, kThreads, 0, stream>>>(
-      static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, rng_states, out_ids,
+      static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       static_cast<Entry*>(scratch), table, status);
   return cudaGetLastError();
 }
 
 cudaError_t launch_sample_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
-    float topp, unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
-    const ExpTable& table, int* status, cudaStream_t stream) {
+    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, void* scratch,
+    int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
   switch (dtype) {
     case kDtypeFloat:
-      return launch_sample_t<float, false>(logits, rows, vocab, row_stride, inv_t, topp, rng_states,
-                                           out_ids, scratch, blocks, table, status, stream);
+      return launch_sample_t<float, false>(logits, rows, vocab, row_stride, inv_t, topp, topk,
+                                           rng_states, out_ids, scratch, blocks, table, status, stream);
     case kDtypeHalf:
-      return launch_sample_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp,
+      return launch_sample_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp, topk,
                                             rng_states, out_ids, scratch, blocks, table, status,
                                             stream);
     case kDtypeBFloat16:
-      return launch_sample_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp,
+      return launch_sample_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp, topk,
                                                   rng_states, out_ids, scratch, blocks, table,
                                                   status, stream);
     default:

@@ -26,12 +26,13 @@ int sample_kernel_max_blocks_per_sm(int dtype);
 
 int sampler_threads();
 
-// temperature != 0: multinomial (topp outside (0,1)) or top-p sampling of every row.
-// rng_states[r] is advanced once per row; out_ids[r] receives the token.
+// temperature != 0: top-k (0 < topk < vocab), else multinomial (topp outside (0,1)) or top-p
+// sampling of every row. rng_states[r] is advanced once per row; out_ids[r] receives the
+// token. Top-k and top-p need `scratch` (sampler_scratch_bytes).
 cudaError_t launch_sample_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
-    float topp, unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
-    const ExpTable& table, int* status, cudaStream_t stream);
+    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, void* scratch,
+    int blocks, const ExpTable& table, int* status, cudaStream_t stream);
 
 // temperature == 0: greedy argmax of every row.
 cudaError_t launch_argmax_rows(

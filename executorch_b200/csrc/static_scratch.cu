@@ -120,7 +120,7 @@ etb200_error_t etb200_sample_rows_static(
     ExpTable table;
     make_exp_table(&table);
     e = launch_sample_rows(dtype, logits_device, rows, vocab_size, row_stride_elems, inv_t, topp,
-                           reinterpret_cast<unsigned long long*>(rng_states_device), out_ids_device,
+                           /*topk=*/0, reinterpret_cast<unsigned long long*>(rng_states_device), out_ids_device,
                            scratch, (int)blocks, table, nullptr, st);
   }
   if (e != cudaSuccess) return fail(ETB200_INTERNAL, cudaGetErrorString(e));

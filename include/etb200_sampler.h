@@ -84,7 +84,8 @@ ETB200_EXPORT etb200_error_t etb200_sampler_destroy(etb200_sampler_t* handle);
 ETB200_EXPORT etb200_error_t etb200_sampler_set_temperature(
     etb200_sampler_t* handle, float temperature);
 
-/* Sampler::set_topk, sampler.h:58-60. k <= 0 or k >= vocab_size disables top-k. */
+/* Sampler::set_topk, sampler.h:58-60. k <= 0 or k >= vocab_size disables top-k; an active
+ * top-k takes precedence over top-p (sampler.cpp:239-241). */
 ETB200_EXPORT etb200_error_t etb200_sampler_set_topk(etb200_sampler_t* handle, int32_t topk);
 
 /* Reads back / replaces the handle's own xorshift64* state (Sampler::rng_state_,

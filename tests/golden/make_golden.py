@@ -70,6 +70,20 @@ def main():
             out[f"{key}_sh{si}"] = shipped.sample_rows(x, t, p, seeds, dtype=cfg.dtype, threads=8)
         meta.append(dict(key=key, kind="workload", name=name, row_ids=ids, settings=sets,
                          sha256=hashlib.sha256(x.tobytes()).hexdigest()))
+    # top-k (sampler.cpp:72-120) on fp32 inputs, where no two probabilities are equal and the
+    # unspecified tie order of std::partial_sort cannot matter
+    for vocab, ks in ((64, (1, 3, 50)), (1000, (1, 40, 999)), (4099, (2, 100))):
+        x = small_inputs(vocab, "fp32", 24, seed=2000 + vocab)
+        seeds = np.arange(24, dtype=np.uint64) * 31 + 5
+        key = f"k{vocab}"
+        out[key + "_x"] = x
+        out[key + "_seeds"] = seeds
+        for k in ks:
+            out[f"{key}_k{k}"] = shipped.sample_rows(x, 0.9, 0.9, seeds, dtype="fp32", topk=k)
+        meta.append(dict(key=key, kind="topk", vocab=vocab, ks=list(ks), temperature=0.9, topp=0.9))
+    x = W.rows_numpy("c1", list(range(100)))
+    out["k_c1_k40"] = shipped.sample_rows(x, 0.8, 0.9, np.arange(100, dtype=np.uint64), dtype="fp32",
+                                          topk=40, threads=8)
     # decode-loop usage: one sampler, evolving state, 64 draws from one row
     row = W.rows_numpy("c3", [5], vocab=8192)[0]
     out["seq_x"] = row

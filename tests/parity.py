@@ -22,10 +22,12 @@ def to_device(x: np.ndarray, dtype: str, device) -> torch.Tensor:
 
 
 def gpu_sample(x: np.ndarray, dtype: str, temperature: float, topp: float, seeds, device,
-               return_states: bool = False):
+               return_states: bool = False, topk: int = 0):
     rows, vocab = x.shape
     s = Sampler(vocab, temperature, topp, 0, device=device)
     try:
+        if topk:
+            s.set_topk(topk)
         t = to_device(x, dtype, device)
         states = seeds_to_states(seeds, device)
         ids = s.sample_rows(t, states)

@@ -273,11 +273,11 @@ def test_mode_selection_setters_and_errors(cuda_device, restatement):
     a = s.sample_rows(t, seeds_to_states(seeds, cuda_device)).cpu().numpy()
     assert np.array_equal(a, restatement.sample_rows(x, 0.5, 0.9, seeds))
     s.set_topk(2048)  # k >= vocab disables top-k (sampler.cpp:239)
-    s.sample_rows(t, seeds_to_states(seeds, cuda_device))
-    s.set_topk(5)
-    with pytest.raises(_lib.SamplerError) as e:
-        s.sample_rows(t, seeds_to_states(seeds, cuda_device))
-    assert e.value.code == _lib.NOT_SUPPORTED
+    a = s.sample_rows(t, seeds_to_states(seeds, cuda_device)).cpu().numpy()
+    assert np.array_equal(a, restatement.sample_rows(x, 0.5, 0.9, seeds))
+    s.set_topk(5)  # top-k takes precedence over top-p (sampler.cpp:239-241)
+    a = s.sample_rows(t, seeds_to_states(seeds, cuda_device)).cpu().numpy()
+    assert np.array_equal(a, restatement.sample_rows(x, 0.5, 0.9, seeds, topk=5))
     s.set_topk(0)
     with pytest.raises(_lib.SamplerError) as e:
         s.sample_rows(t.to(torch.float64))
@@ -298,6 +298,76 @@ def test_mode_selection_setters_and_errors(cuda_device, restatement):
     assert np.array_equal(sample_all_from_logits(t3, s).cpu().numpy(),
                           restatement.sample_rows(x, 0.0, 0.9, seeds))
     s.close()
+
+
+def test_topk_reference_test_cases(cuda_device):
+    """The five top-k tests of extension/llm/sampler/test/test_sampler.cpp:45-154."""
+    # TestTopKRestrictsToCandidates
+    s = Sampler(100, 1.0, 0.0, 42, device=cuda_device)
+    s.set_topk(3)
+    x = torch.full((100,), -10.0, device=cuda_device)
+    x[7], x[13], x[42] = 5.0, 4.5, 4.0
+    assert {s.sample(x) for _ in range(50)} <= {7, 13, 42}
+    s.close()
+    # TestTopKDisabledByZero
+    s = Sampler(50, 1.0, 0.0, 7, device=cuda_device)
+    s.set_topk(0)
+    x = torch.full((50,), -10.0, device=cuda_device)
+    x[11] = 20.0
+    assert sum(s.sample(x) == 11 for _ in range(20)) >= 18
+    s.close()
+    # TestTopKWithFP16
+    s = Sampler(50, 1.0, 0.0, 99, device=cuda_device)
+    s.set_topk(2)
+    x = torch.full((50,), -10.0, device=cuda_device, dtype=torch.float16)
+    x[3], x[8] = 5.0, 4.5
+    assert {s.sample(x) for _ in range(30)} <= {3, 8}
+    s.close()
+    # TestTopKEqualsOneIsArgmax
+    s = Sampler(100, 1.0, 0.0, 123, device=cuda_device)
+    s.set_topk(1)
+    x = torch.rand(100, device=cuda_device)
+    x[57] = 100.0
+    assert all(s.sample(x) == 57 for _ in range(10))
+    s.close()
+    # TestTopKTakesPrecedenceOverTopP
+    s = Sampler(100, 1.0, 0.99, 99, device=cuda_device)
+    s.set_topk(2)
+    x = torch.full((100,), -10.0, device=cuda_device)
+    x[3], x[8], x[19] = 5.0, 4.5, 4.0
+    assert {s.sample(x) for _ in range(50)} <= {3, 8}
+    s.close()
+
+
+def test_topk_parity(cuda_device, restatement, golden):
+    z, meta = golden
+    # tokens of the reference's own compiled sampler (fp32: no equal probabilities)
+    for m in meta:
+        if m["kind"] != "topk":
+            continue
+        x, seeds = z[m["key"] + "_x"], z[m["key"] + "_seeds"]
+        for k in m["ks"]:
+            got = gpu_sample(x, "fp32", m["temperature"], m["topp"], seeds, cuda_device, topk=k)
+            assert np.array_equal(got, z[f"{m['key']}_k{k}"]), (m["vocab"], k)
+    x = W.rows_numpy("c1", list(range(100)))
+    got = gpu_sample(x, "fp32", 0.8, 0.9, np.arange(100, dtype=np.uint64), cuda_device, topk=40)
+    assert np.array_equal(got, z["k_c1_k40"])
+    # against the oracle (ties pinned to index order) on the benchmark-shaped rows
+    for name, ids, ks in (("c1", range(300), (1, 40, 5000)), ("c3", range(64), (1, 50, 4000)),
+                          ("c4", [0, 1, 2048, 2049], (8, 20000)), ("c5", range(16), (64,))):
+        cfg = W.CONFIGS[name]
+        x = W.rows_numpy(name, list(ids))
+        seeds = np.asarray(list(ids), dtype=np.uint64) + 17
+        for k in ks:
+            want = restatement.sample_rows(x, cfg.temperature, cfg.topp, seeds, dtype=cfg.dtype, topk=k,
+                                           threads=8)
+            got = gpu_sample(x, cfg.dtype, cfg.temperature, cfg.topp, seeds, cuda_device, topk=k)
+            assert np.array_equal(got, want), (name, k, np.nonzero(got != want)[0][:8])
+    # low temperature: most exponentials underflow to 0, fewer than k entries are positive
+    x = W.rows_numpy("c1", list(range(16)), vocab=4096)
+    seeds = np.arange(16, dtype=np.uint64) + 3
+    want = restatement.sample_rows(x, 0.05, 0.9, seeds, topk=3000)
+    assert np.array_equal(gpu_sample(x, "fp32", 0.05, 0.9, seeds, cuda_device, topk=3000), want)
 
 
 def test_host_buffer_entry_matches_device_entry(cuda_device, restatement):

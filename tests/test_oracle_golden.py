@@ -93,6 +93,20 @@ def test_workload_cases_match_reference_tokens(restatement, golden):
             assert np.array_equal(got, z[f"w_{m['name']}_st{si}"]), (m["name"], t, p)
 
 
+def test_topk_matches_reference_tokens(restatement, golden):
+    z, meta = golden
+    for m in meta:
+        if m["kind"] != "topk":
+            continue
+        x, seeds = z[m["key"] + "_x"], z[m["key"] + "_seeds"]
+        for k in m["ks"]:
+            got = restatement.sample_rows(x, m["temperature"], m["topp"], seeds, topk=k)
+            assert np.array_equal(got, z[f"{m['key']}_k{k}"]), (m["vocab"], k)
+    x = W.rows_numpy("c1", list(range(100)))
+    got = restatement.sample_rows(x, 0.8, 0.9, np.arange(100, dtype=np.uint64), topk=40)
+    assert np.array_equal(got, z["k_c1_k40"])
+
+
 def test_decode_loop_sequence(restatement, golden):
     z, _ = golden
     row = W.bf16_bits_to_f32(z["seq_x"])
