@@ -259,23 +259,35 @@ ETB_HD void seq_push_scaled(SeqSummary* s, float v, float inv_u) {
   if (s->a1 > kSeqSat) s->a1 = kSeqSat;
 }
 
-// Tie-free fast variant of seq_push_scaled: adds round_half_even(v / u) to *acc and returns
-// true when v / u lies exactly half-way between two integers (then the caller must redo the
-// chunk with the two-parity functions, because the result depends on the parity of N).
-// v / u is clamped to 2^24; any chunk containing such a term leaves the binade anyway.
-ETB_HD bool seq_push_fast(int* acc, float v, float inv_u) {
+// Tie-free fast variant of seq_push_scaled: adds round_half_even(v / u) to *acc and
+// multiplies *tie_prod by (|rounding error| - 1/2), which is exactly zero when v / u lies
+// half-way between two integers (then the caller must redo the chunk with the two-parity
+// functions, because the result depends on the parity of N). A product that underflows to
+// zero without a real tie only costs that redo. v / u is clamped to 2^24; any chunk
+// containing such a term leaves the binade anyway. `inv_u24` is 2^-24 / u.
+//
+// Written so that everything but the integer add is a float multiply or add: on the GPU the
+// integer/compare pipe is the scarce one.
+ETB_HD void seq_push_fast(int* acc, float* tie_prod, float v, float inv_u24) {
 #if defined(__CUDA_ARCH__)
-  const float t = fminf(__fmul_rn(v, inv_u), 16777216.0f);
+  const float t = __fmul_rn(__saturatef(__fmul_rn(v, inv_u24)), 16777216.0f);
   const float tm = __fadd_rn(t, 8388608.0f);  // 2^23: the sum's low bits are the rounded t
   const float d = __fsub_rn(t, __fsub_rn(tm, 8388608.0f));
+  *tie_prod = __fmul_rn(*tie_prod, __fsub_rn(fabsf(d), 0.5f));
 #else
-  float t = v * inv_u;
-  t = t < 16777216.0f ? t : 16777216.0f;
+  float c = v * inv_u24;
+  c = c < 0.0f ? 0.0f : (c > 1.0f ? 1.0f : c);
+  const float t = c * 16777216.0f;
   const float tm = t + 8388608.0f;
   const float d = t - (tm - 8388608.0f);
+  *tie_prod = *tie_prod * (fabsf(d) - 0.5f);
 #endif
   *acc += (int)(f32_bits(tm) - 0x4B000000u);
-  return d == 0.5f || d == -0.5f;
+}
+
+// 2^(126 - kb): 2^-24 / u as a float, representable for kb in [27, 252].
+ETB_HD float seq_inv_u24(int kb) {
+  return bits_f32((uint32_t)(126 - kb + 127) << 23);
 }
 
 // 2^(150 - kb) as a float when representable as a normal number (kb in [24, 150+126]); the

@@ -180,18 +180,19 @@ __device__ __forceinline__ bool seqsum_tile(
     seq_identity(&mine);
     const bool active = tid >= consumed;
     if (active) {
-      if (kb >= 27) {
+      if (kb >= 27 && kb <= 252) {
         // v / u by an exact power-of-two scaling; adding 2^23 rounds it to an integer
         // (half to even) that can be read off the sum's bit pattern
-        const float inv_u = seq_inv_u(kb);
+        const float inv_u24 = seq_inv_u24(kb);
         int acc = 0;
-        bool tie = false;
+        float tie_prod = 1.0f;
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) tie = seq_push_fast(&acc, v[j], inv_u) || tie;
+        for (int j = 0; j < kChunk; ++j) seq_push_fast(&acc, &tie_prod, v[j], inv_u24);
         acc = acc < kFastSat ? acc : kFastSat;
         mine.a0 = acc;
         mine.a1 = acc;
-        if (tie) {
+        if (!(tie_prod != 0.0f)) {  // zero (a tie, or an underflowed product) or NaN
+          const float inv_u = seq_inv_u(kb);
           seq_identity(&mine);
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) seq_push_scaled(&mine, v[j], inv_u);

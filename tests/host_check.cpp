@@ -25,15 +25,16 @@ bool tile(const float* v, int threads, int chunk, float& s, bool search, float t
     for (int t = 0; t < threads; ++t) {
       seq_identity(&mine[t]);
       if (t >= consumed) {
-        if (kb >= 27 && !force_generic) {
+        if (kb >= 27 && kb <= 252 && !force_generic) {
           // as the kernel: tie-free fast path first, two-parity redo of the chunk on a tie
-          const float inv_u = seq_inv_u(kb);
+          const float inv_u24 = seq_inv_u24(kb);
           int acc = 0;
-          bool tie = false;
-          for (int j = 0; j < chunk; ++j) tie = seq_push_fast(&acc, v[t * chunk + j], inv_u) || tie;
+          float tie_prod = 1.0f;
+          for (int j = 0; j < chunk; ++j) seq_push_fast(&acc, &tie_prod, v[t * chunk + j], inv_u24);
           if (acc > (1 << 25)) acc = 1 << 25;
           mine[t].a0 = mine[t].a1 = acc;
-          if (tie) {
+          if (!(tie_prod != 0.0f)) {
+            const float inv_u = seq_inv_u(kb);
             seq_identity(&mine[t]);
             for (int j = 0; j < chunk; ++j) seq_push_scaled(&mine[t], v[t * chunk + j], inv_u);
           }
