@@ -2,7 +2,8 @@
 (extension/llm/sampler). CUDA only; see include/etb200_sampler.h for the C ABI."""
 
 __all__ = ["Sampler", "sample_from_logits", "sample_all_from_logits", "logits_to_token",
-           "seeds_to_states", "ShardedSampler", "shard_rows"]
+           "seeds_to_states", "ShardedSampler", "shard_rows", "LogitProcessor",
+           "apply_logit_processors", "TokenGenerator"]
 
 
 def __getattr__(name):
@@ -13,4 +14,7 @@ def __getattr__(name):
     if name in ("ShardedSampler", "shard_rows"):
         from . import sharded
         return getattr(sharded, name)
+    if name in ("LogitProcessor", "apply_logit_processors", "TokenGenerator"):
+        from . import generator
+        return getattr(generator, name)
     raise AttributeError(name)

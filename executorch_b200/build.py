@@ -57,5 +57,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+PYBIND = os.path.join(LIBDIR, "_sampler_pybind" + (__import__("sysconfig").get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_pybind(force: bool = False) -> str:
+    """Builds the pybind11 module over the C++ Sampler class (g++; links the CUDA library)."""
+    import sysconfig
+
+    import pybind11
+
+    src = os.path.join(CSRC, "pybind.cpp")
+    hpp = os.path.join(PKG, "..", "include", "etb200_sampler.hpp")
+    if (not force and os.path.exists(PYBIND)
+            and os.path.getmtime(PYBIND) > max(os.path.getmtime(src), os.path.getmtime(hpp), os.path.getmtime(LIB))):
+        return PYBIND
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden",
+           "-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], src,
+           "-L" + LIBDIR, "-letb200_sampler", "-Wl,-rpath,$ORIGIN", "-o", PYBIND]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return PYBIND
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_pybind(force="--force" in sys.argv))

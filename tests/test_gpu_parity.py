@@ -370,6 +370,34 @@ def test_topk_parity(cuda_device, restatement, golden):
     assert np.array_equal(gpu_sample(x, "fp32", 0.05, 0.9, seeds, cuda_device, topk=3000), want)
 
 
+def test_pybind_module_drives_the_same_kernels(cuda_device, restatement):
+    import sys
+    libdir = os.path.join(ROOT, "executorch_b200", "lib")
+    sys.path.insert(0, libdir)
+    try:
+        import _sampler_pybind as m
+    finally:
+        sys.path.remove(libdir)
+    x = W.rows_numpy("c3", list(range(12)), vocab=20000)
+    t = to_device(x, "bf16", cuda_device)
+    seeds = np.arange(12, dtype=np.uint64) + 9
+    states = seeds_to_states(seeds, cuda_device)
+    out = torch.empty(12, dtype=torch.int64, device=cuda_device)
+    s = m.Sampler(20000, 0.7, 0.9, 5, cuda_device.index)
+    stream = torch.cuda.current_stream().cuda_stream
+    s.sample_rows(t.data_ptr(), _lib.DTYPE_BFLOAT16, 12, t.stride(0), states.data_ptr(), out.data_ptr(), stream)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), restatement.sample_rows(x, 0.7, 0.9, seeds, dtype="bf16"))
+    # single-row sample() with the sampler's own state (seed 5), three draws
+    want = restatement.sample_sequence(W.to_f32(x[:1], "bf16")[0], 0.7, 0.9, 5, 3)
+    got = [s.sample(t[0].data_ptr(), _lib.DTYPE_BFLOAT16, stream) for _ in range(3)]
+    assert got == list(want)
+    s.set_topk(7)
+    s.rng_state = 77
+    want = restatement.sample_rows(x[:1], 0.7, 0.9, np.array([77], dtype=np.uint64), dtype="bf16", topk=7)
+    assert s.sample(t[0].data_ptr(), _lib.DTYPE_BFLOAT16, stream) == want[0]
+
+
 def test_host_buffer_entry_matches_device_entry(cuda_device, restatement):
     x = W.rows_numpy("c3", list(range(16)), vocab=16384)
     seeds = np.arange(16, dtype=np.uint64) + 5
