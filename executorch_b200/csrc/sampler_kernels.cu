@@ -51,6 +51,7 @@ constexpr int kRadixBits = 8;
 constexpr int kRadix = 1 << kRadixBits;
 constexpr int kFastSat = 1 << 25;           // per-thread clamp of chunk summaries
 constexpr int kCompactSteps = 448;          // list entries compacted per segment = 448 * kThreads
+constexpr float kGuessFloor = 1.0f / 8192.0f;  // first guess of a floor under the values that matter
 constexpr int kListBatch = 8;               // list entries a thread loads before using any of them
 constexpr int kRankSortMax = 512;           // survivor lists up to this size are rank-sorted in shared memory
 
@@ -653,6 +654,265 @@ __device__ bool list_search(
 }
 
 // ---------------------------------------------------------------------------------------
+// Pieces of the top-p / top-k tail. All are block-wide and return block-uniform results.
+// ---------------------------------------------------------------------------------------
+
+// Bins the values of list A and picks the lowest value bin to keep: the largest bin b such
+// that the bins >= b surely hold more than topp of the mass (top-p; the margin covers the
+// rounding of the reference's own running sum) or at least topk entries (top-k). Returns
+// false when even all listed entries do not suffice. *bin_out is 0 ("keep everything
+// listed") in that case. *cnt_out = entries in the kept bins.
+template <typename S>
+__device__ bool pick_value_threshold(
+    S& sm, const Entry* listA, int n_a, float sum, float topp, int topk, bool use_topk,
+    int* bin_out, int* cnt_out) {
+  const int tid = threadIdx.x, warp = tid >> 5;
+  __syncthreads();  // earlier users of the union are done
+  // per-warp integer counters, filled by one coalesced pass over the list
+  for (int b = tid; b < kWarps * kBins * 2; b += kThreads) (&sm.u.wbins[0][0][0])[b] = 0;
+  __syncthreads();
+  for (int i0 = 0; i0 < n_a; i0 += kListBatch * kThreads) {
+    uint32_t k[kListBatch];
+#pragma unroll
+    for (int u = 0; u < kListBatch; ++u) {  // independent loads first, so they overlap
+      const int i = i0 + u * kThreads + tid;
+      k[u] = i < n_a ? listA[i].key : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < kListBatch; ++u) {
+      if (i0 + u * kThreads + tid < n_a) {
+        int bin = (int)(k[u] >> kBinShift) - kBinBase;
+        bin = bin < 0 ? 0 : (bin < kBins ? bin : kBins - 1);
+        atomicAdd(&sm.u.wbins[warp][bin][0], 1u);
+        atomicAdd(&sm.u.wbins[warp][bin][1], (k[u] >> 8) & 0x1FFFu);
+      }
+    }
+  }
+  __syncthreads();
+  // Per-bin counts and the mass they hold, slightly rounded down: a value whose bits are
+  // (bin << 21 | off) equals edge(bin) + off * 2^(exponent - 23), and off was accumulated with
+  // its top 13 bits only. Bin 0 also holds everything below the covered range, so its mass
+  // counts as 0.
+  if (tid < kBins) {
+    unsigned c = 0, o = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      c += sm.u.wbins[w][tid][0];
+      o += sm.u.wbins[w][tid][1];
+    }
+    const uint32_t edge_bits = (uint32_t)(tid + kBinBase) << kBinShift;
+    const float edge = bits_f32(edge_bits);
+    // one unit of the 13-bit offset is 2^8 units of the last place of the bin's binade
+    const float unit = bits_f32(edge_bits & 0x7F800000u) * (256.0f / 8388608.0f);
+    sm.hcnt[tid] = c;
+    sm.hmass[tid] = tid == 0 ? 0.0f : (float)c * edge + (float)o * unit;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    float acc = 0.0f;
+    unsigned cacc = 0;
+    int chosen = 0, chosen_cnt = n_a;
+    bool done = false;
+    for (int hi = kBins - 1; hi >= 0 && !done; hi -= 32) {
+      const int b = hi - tid;
+      float m = (b >= 0) ? sm.hmass[b] : 0.0f;
+      unsigned c = (b >= 0) ? sm.hcnt[b] : 0u;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float om = __shfl_up_sync(0xffffffffu, m, d);
+        const unsigned oc = __shfl_up_sync(0xffffffffu, c, d);
+        if (tid >= d) {
+          m += om;
+          c += oc;
+        }
+      }
+      const float mass_above = acc + m;
+      const float cnt_above = (float)(cacc + c);
+      const float need = sum * (topp * 1.002f + 0.001f + cnt_above * 4.8e-7f);
+      // bin 0 is unbounded below, so it never counts as "above" anything
+      const bool enough = b > 0 && (use_topk ? (cacc + c >= (unsigned)topk) : (mass_above >= need));
+      const unsigned ok = __ballot_sync(0xffffffffu, enough);
+      if (ok) {
+        const int sel = __ffs(ok) - 1;
+        chosen = hi - sel;
+        chosen_cnt = (int)(cacc + __shfl_sync(0xffffffffu, c, sel));
+        done = true;
+      }
+      acc += __shfl_sync(0xffffffffu, m, 31);
+      cacc += __shfl_sync(0xffffffffu, c, 31);
+    }
+    if (tid == 0) {
+      sm.misc_i[1] = chosen;
+      sm.misc_i[2] = done ? 1 : 0;
+      sm.misc_i[3] = chosen_cnt;
+    }
+  }
+  __syncthreads();
+  *bin_out = sm.misc_i[1];
+  *cnt_out = sm.misc_i[3];
+  return sm.misc_i[2] != 0;
+}
+
+// Lists every entry of the row with e >= floor into list A, in index order. Returns the count.
+template <typename T, typename S>
+__device__ int gather_candidates(const RowMath<T, S>& rm, S& sm, Entry* listA, float floor) {
+  const int tid = threadIdx.x;
+  int n_a = 0;
+  for (int base = 0; base < rm.vocab; base += kTile) {
+    const int i0 = base + tid * kChunk;
+    float e[kChunk];
+    rm.chunk(i0, sm, e);  // 0 beyond the row, and floor > 0
+    int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) cnt += (e[j] >= floor) ? 1 : 0;
+    int tot;
+    int off = n_a + block_excl_count(sm, cnt, &tot);
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) {
+      if (e[j] >= floor) {
+        Entry en;
+        en.key = f32_bits(e[j]);
+        en.idx = i0 + j;
+        listA[off++] = en;
+      }
+    }
+    n_a += tot;
+  }
+  __threadfence_block();
+  __syncthreads();
+  return n_a;
+}
+
+// Compacts list A into list B, in list order: entries with key >= key_lo whose probability
+// e / sum passes the cutoff crop (sampler.cpp:136-143; no crop for top-k). List B holds the
+// probabilities' bits. Two coalesced passes over list A per segment of kCompactSteps *
+// kThreads entries: count the survivors of every (step, warp), prefix those counts, then
+// write the survivors. Returns the number of survivors.
+template <typename S>
+__device__ int compact_candidates(
+    S& sm, const Entry* listA, int n_a, Entry* listB, uint32_t key_lo, float sum, float cutoff,
+    bool use_topk) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int n_b = 0;
+  for (int seg0 = 0; seg0 < n_a; seg0 += kCompactSteps * kThreads) {
+    const int seg_n = (n_a - seg0) < kCompactSteps * kThreads ? (n_a - seg0) : kCompactSteps * kThreads;
+    const int steps = (seg_n + kThreads - 1) / kThreads;
+    __syncthreads();  // earlier users of the union are done
+    for (int st0 = 0; st0 < steps; st0 += kListBatch) {
+      uint32_t k[kListBatch];
+#pragma unroll
+      for (int u = 0; u < kListBatch; ++u) {
+        const int i = seg0 + (st0 + u) * kThreads + tid;
+        k[u] = (st0 + u < steps && i < n_a) ? listA[i].key : 0u;
+      }
+#pragma unroll
+      for (int u = 0; u < kListBatch; ++u) {
+        if (st0 + u < steps) {  // block-uniform
+          const int i = seg0 + (st0 + u) * kThreads + tid;
+          const bool keep = i < n_a && k[u] >= key_lo &&
+                            (use_topk || __fdiv_rn(bits_f32(k[u]), sum) >= cutoff);
+          const unsigned kbal = __ballot_sync(0xffffffffu, keep);
+          if (lane == 0) sm.u.compact.cnt[st0 + u][warp] = (unsigned short)__popc(kbal);
+        }
+      }
+    }
+    __syncthreads();
+    // thread t owns step t: exclusive prefix inside the step, and the step total
+    int step_total = 0;
+    if (tid < steps) {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const int c = sm.u.compact.cnt[tid][w];
+        sm.u.compact.cnt[tid][w] = (unsigned short)step_total;
+        step_total += c;
+      }
+    }
+    int seg_total;
+    const int step_base = block_excl_count(sm, step_total, &seg_total);
+    if (tid < steps) sm.u.compact.base[tid] = (unsigned)(n_b + step_base);
+    __syncthreads();
+    for (int st0 = 0; st0 < steps; st0 += kListBatch) {
+      Entry en[kListBatch];
+#pragma unroll
+      for (int u = 0; u < kListBatch; ++u) {
+        const int i = seg0 + (st0 + u) * kThreads + tid;
+        en[u].key = 0;
+        en[u].idx = 0;
+        if (st0 + u < steps && i < n_a) en[u] = listA[i];
+      }
+#pragma unroll
+      for (int u = 0; u < kListBatch; ++u) {
+        if (st0 + u < steps) {  // block-uniform
+          const int i = seg0 + (st0 + u) * kThreads + tid;
+          bool keep = false;
+          if (i < n_a && en[u].key >= key_lo) {
+            const float p = __fdiv_rn(bits_f32(en[u].key), sum);
+            keep = use_topk || p >= cutoff;
+            en[u].key = f32_bits(p);
+          }
+          const unsigned kbal = __ballot_sync(0xffffffffu, keep);
+          if (keep) {
+            listB[sm.u.compact.base[st0 + u] + sm.u.compact.cnt[st0 + u][warp] +
+                  __popc(kbal & ((1u << lane) - 1u))] = en[u];
+          }
+        }
+      }
+    }
+    n_b += seg_total;
+  }
+  __threadfence_block();
+  __syncthreads();
+  return n_b;
+}
+
+// Sorts list B by probability, descending; equal probabilities end up in index order. Small
+// lists are rank-sorted in shared memory; larger ones take four stable LSD radix passes that
+// ping-pong between list B and `spare` (after an even number of passes the result is back in
+// list B).
+template <typename S>
+__device__ void sort_candidates(S& sm, Entry* listB, int n_b, Entry* spare) {
+  const int tid = threadIdx.x;
+  if (n_b <= kRankSortMax) {
+    // Composite key = (probability bits, inverted index): larger means earlier in the sorted
+    // order. kThreads / kRankSortMax threads share an entry, each scanning a part of the list.
+    const int ent = tid & (kRankSortMax - 1), part = tid / kRankSortMax;
+    Entry en;
+    en.key = 0;
+    en.idx = 0;
+    if (tid < n_b) {
+      en = listB[tid];
+      sm.u.rsort.ck[tid] = ((unsigned long long)en.key << 32) | (uint32_t)(0x7FFFFFFF - en.idx);
+      sm.u.rsort.rank[tid] = 0;
+    }
+    __syncthreads();
+    if (ent < n_b) {
+      const unsigned long long mine = sm.u.rsort.ck[ent];
+      constexpr int kParts = kThreads / kRankSortMax;
+      const int per = (n_b + kParts - 1) / kParts;
+      const int j0 = part * per, j1 = (j0 + per) < n_b ? (j0 + per) : n_b;
+      int rank = 0;
+#pragma unroll 8
+      for (int j = j0; j < j1; ++j) rank += sm.u.rsort.ck[j] > mine ? 1 : 0;
+      atomicAdd(&sm.u.rsort.rank[ent], rank);
+    }
+    __syncthreads();
+    if (tid < n_b) listB[sm.u.rsort.rank[tid]] = en;
+    __threadfence_block();
+  } else {
+    Entry* ping = listB;
+    Entry* pong = spare;
+    for (int pass = 0; pass < 32 / kRadixBits; ++pass) {
+      radix_pass_desc(sm, ping, pong, n_b, pass * kRadixBits);
+      __threadfence_block();
+      Entry* t = ping;
+      ping = pong;
+      pong = t;
+    }
+  }
+  __syncthreads();
+}
+
+// ---------------------------------------------------------------------------------------
 // The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
 // otherwise. Follows Sampler::sample<float> (sampler.cpp:222-251).
 // ---------------------------------------------------------------------------------------
@@ -671,6 +931,10 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     sm.two_parity[tid] = 0;
   }
   int rp = 0;  // which set of scan-round slots the next round uses (see seqsum_tile)
+  // Guessed floor under the values that matter (nucleus members / the k largest). Pass 2 lists
+  // only e >= guess; if that turns out to be too high for a row, the row is regathered with
+  // its exact floor and the guess is lowered for the block's later rows.
+  float guess = kGuessFloor;
   __syncthreads();
   // mode selection of Sampler::sample (sampler.cpp:239-248): top-k wins over top-p
   const bool use_topk = topk > 0 && topk < vocab;
@@ -706,8 +970,10 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     // sampler.cpp:136-143: p_i >= cutoff needs e_i >= cutoff * S and S >= 1 (the maximum
     // contributes exactly 1), so e_i >= cutoff * (1 - 1e-6) is necessary.
     const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
-    // Top-k has no crop: it lists every entry with e > 0 (the smallest positive float as floor).
-    const float e_floor = use_topp ? cutoff * 0.999999f : (use_topk ? 1.4e-45f : 0.0f);
+    // Top-k has no crop: its exact floor is "e > 0". Both modes list only e >= max(exact
+    // floor, guess) here and verify afterwards that this was enough.
+    const float exact_floor0 = use_topp ? cutoff * 0.999999f : 1.4e-45f;
+    const float e_floor = use_list ? fmaxf(exact_floor0, guess) : 0.0f;
     float s = 0.0f;
     int n_a = 0;
     {
@@ -771,6 +1037,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       }
       // p_i >= cutoff needs e_i >= cutoff * S, and S is at least the running sum so far
       const float floor_now = use_topp ? fmaxf(e_floor, cutoff * s * 0.999999f) : e_floor;
+      (void)exact_floor0;
       int cnt = 0, inc = 0;
       if (use_list) {
         // entries beyond the row are 0 and the floor is > 0, so they never count
@@ -841,242 +1108,77 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       // ---- pass 3b: sample_topp (sampler.cpp:122-171) or sample_topk (sampler.cpp:72-120)
       __threadfence_block();
       __syncthreads();
-      // value bins of the listed candidates: per-warp integer counters, filled by one
-      // coalesced pass over the list (every lane busy, unlike binning inside pass 2)
-      for (int b = tid; b < kWarps * kBins * 2; b += kThreads) (&sm.u.wbins[0][0][0])[b] = 0;
-      __syncthreads();
-      for (int i0 = 0; i0 < n_a; i0 += kListBatch * kThreads) {
-        uint32_t k[kListBatch];
-#pragma unroll
-        for (int u = 0; u < kListBatch; ++u) {  // independent loads first, so they overlap
-          const int i = i0 + u * kThreads + tid;
-          k[u] = i < n_a ? listA[i].key : 0u;
-        }
-#pragma unroll
-        for (int u = 0; u < kListBatch; ++u) {
-          if (i0 + u * kThreads + tid < n_a) {
-            int bin = (int)(k[u] >> kBinShift) - kBinBase;
-            bin = bin < 0 ? 0 : (bin < kBins ? bin : kBins - 1);
-            atomicAdd(&sm.u.wbins[warp][bin][0], 1u);
-            atomicAdd(&sm.u.wbins[warp][bin][1], (k[u] >> 8) & 0x1FFFu);
-          }
-        }
-      }
-      __syncthreads();
-      // Per-bin counts of the listed values and the mass they hold, slightly rounded down: a
-      // value whose bits are (bin << 21 | off) equals edge(bin) + off * 2^(exponent - 23), and
-      // off was accumulated with its top 13 bits only. Bin 0 also holds everything below the
-      // covered range, so its mass counts as 0.
-      if (tid < kBins) {
-        unsigned c = 0, o = 0;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-          c += sm.u.wbins[w][tid][0];
-          o += sm.u.wbins[w][tid][1];
-        }
-        const uint32_t edge_bits = (uint32_t)(tid + kBinBase) << kBinShift;
-        const float edge = bits_f32(edge_bits);
-        // one unit of the 13-bit offset is 2^8 units of the last place of the bin's binade
-        const float unit = bits_f32(edge_bits & 0x7F800000u) * (256.0f / 8388608.0f);
-        sm.hcnt[tid] = c;
-        sm.hmass[tid] = tid == 0 ? 0.0f : (float)c * edge + (float)o * unit;
-      }
-      __syncthreads();
-      // Lowest bin to keep: the largest b whose bins >= b surely hold more than topp of the
-      // mass. The margin covers the rounding of the reference's own running sum; the choice
-      // only has to be safe, not tight, and is verified below.
-      if (tid < 32) {
-        float acc = 0.0f;
-        unsigned cacc = 0;
-        int chosen = 0, chosen_cnt = 0;
-        bool done = false;
-        for (int hi = kBins - 1; hi >= 0 && !done; hi -= 32) {
-          const int b = hi - tid;
-          float m = (b >= 0) ? sm.hmass[b] : 0.0f;
-          unsigned c = (b >= 0) ? sm.hcnt[b] : 0u;
-#pragma unroll
-          for (int d = 1; d < 32; d <<= 1) {
-            const float om = __shfl_up_sync(0xffffffffu, m, d);
-            const unsigned oc = __shfl_up_sync(0xffffffffu, c, d);
-            if (tid >= d) {
-              m += om;
-              c += oc;
-            }
-          }
-          const float mass_above = acc + m;
-          const float cnt_above = (float)(cacc + c);
-          const float need = sum * (topp * 1.002f + 0.001f + cnt_above * 4.8e-7f);
-          // top-p: enough mass above; top-k: at least k entries above (bin 0 is unbounded below)
-          const bool enough = use_topk ? (b > 0 && cacc + c >= (unsigned)topk) : (mass_above >= need);
-          const unsigned ok = __ballot_sync(0xffffffffu, b >= 0 && enough);
-          if (ok) {
-            const int sel = __ffs(ok) - 1;
-            chosen = hi - sel;
-            chosen_cnt = (int)(cacc + __shfl_sync(0xffffffffu, c, sel));
-            done = true;
-          }
-          acc += __shfl_sync(0xffffffffu, m, 31);
-          cacc += __shfl_sync(0xffffffffu, c, 31);
-        }
-        if (tid == 0) {
-          // The sort below ping-pongs into the free space behind list A, which must hold the
-          // survivors; if it cannot, take the complete candidate set (then list A may be
-          // overwritten because no second attempt is ever needed). Top-k never needs a second
-          // attempt: its threshold is an exact count.
-          if (!done || (!use_topk && n_a + chosen_cnt > vocab)) chosen = 0;
-          sm.misc_i[1] = chosen;
-        }
-      }
-      __syncthreads();
-      int bin_lo = sm.misc_i[1];
-      int n_b = 0;
-      bool have = false;
-      int last_idx = 0;
+      // List A holds every entry with e >= max(exact floor, guess) ("complete" when the guess
+      // was not above the exact floor). Each round: pick a value threshold from the bins,
+      // compact, sort, and replay the reference's cumulative sums; a round that cannot
+      // succeed first completes the list (regather with the exact floor, now that S is known)
+      // and then widens the threshold to everything listed.
+      const float exact_floor = use_topp ? cutoff * sum * 0.999999f : 1.4e-45f;
+      bool complete = e_floor <= exact_floor;
+      bool take_all = false;
+      int n_b = 0, last_idx = 0;
       float cum = 0.0f;
-      for (int attempt = 0; attempt < 2 && !have; ++attempt) {
-        // compact list A -> list B: survivors of the value threshold that pass the cutoff
-        // crop, with their probabilities, still in index order
+      bool have = false;
+      for (int round = 0; round < 4 && !have; ++round) {
+        int bin_lo = 0, kept = n_a;
+        bool enough = true;
+        if (!take_all) enough = pick_value_threshold(sm, listA, n_a, sum, topp, topk, use_topk, &bin_lo, &kept);
+        if (!enough && !complete) {
+          guess = fmaxf(guess * 0.0625f, 1e-30f);  // later rows of this block start lower
+          n_a = gather_candidates(rm, sm, listA, exact_floor);
+          complete = true;
+          continue;
+        }
+        // The radix sort ping-pongs into the free space behind list A. If the survivors may
+        // not fit there, list A itself is the spare buffer, which is only allowed when list A
+        // will not be needed again: make this the final round by taking everything listed
+        // from a complete list.
+        bool spare_is_list_a = false;
+        if (n_a + kept > vocab) {
+          if (!complete) {
+            n_a = gather_candidates(rm, sm, listA, exact_floor);
+            complete = true;
+            continue;
+          }
+          if (!use_topk) bin_lo = 0;  // top-k's count threshold is exact: no later round either way
+          spare_is_list_a = true;
+        }
         const uint32_t key_lo = bin_lo > 0 ? (uint32_t)(bin_lo + kBinBase) << kBinShift : 0u;
-        // Two coalesced passes over list A per segment of kCompactSteps * kThreads entries:
-        // count the survivors of every (step, warp), prefix those counts, then write the
-        // survivors in list order.
-        n_b = 0;
-        for (int seg0 = 0; seg0 < n_a; seg0 += kCompactSteps * kThreads) {
-          const int seg_n = (n_a - seg0) < kCompactSteps * kThreads ? (n_a - seg0) : kCompactSteps * kThreads;
-          const int steps = (seg_n + kThreads - 1) / kThreads;
-          __syncthreads();  // earlier users of the union are done
-          for (int st0 = 0; st0 < steps; st0 += kListBatch) {
-            uint32_t k[kListBatch];
-#pragma unroll
-            for (int u = 0; u < kListBatch; ++u) {
-              const int i = seg0 + (st0 + u) * kThreads + tid;
-              k[u] = (st0 + u < steps && i < n_a) ? listA[i].key : 0u;
-            }
-#pragma unroll
-            for (int u = 0; u < kListBatch; ++u) {
-              if (st0 + u < steps) {  // block-uniform
-                const int i = seg0 + (st0 + u) * kThreads + tid;
-                const bool keep = i < n_a && k[u] >= key_lo &&
-                                  (use_topk || __fdiv_rn(bits_f32(k[u]), sum) >= cutoff);
-                const unsigned kbal = __ballot_sync(0xffffffffu, keep);
-                if (lane == 0) sm.u.compact.cnt[st0 + u][warp] = (unsigned short)__popc(kbal);
-              }
-            }
-          }
-          __syncthreads();
-          // thread t owns step t: exclusive prefix inside the step, and the step total
-          int step_total = 0;
-          if (tid < steps) {
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-              const int c = sm.u.compact.cnt[tid][w];
-              sm.u.compact.cnt[tid][w] = (unsigned short)step_total;
-              step_total += c;
-            }
-          }
-          int seg_total;
-          const int step_base = block_excl_count(sm, step_total, &seg_total);
-          if (tid < steps) sm.u.compact.base[tid] = (unsigned)(n_b + step_base);
-          __syncthreads();
-          for (int st0 = 0; st0 < steps; st0 += kListBatch) {
-            Entry en[kListBatch];
-#pragma unroll
-            for (int u = 0; u < kListBatch; ++u) {
-              const int i = seg0 + (st0 + u) * kThreads + tid;
-              en[u].key = 0;
-              en[u].idx = 0;
-              if (st0 + u < steps && i < n_a) en[u] = listA[i];
-            }
-#pragma unroll
-            for (int u = 0; u < kListBatch; ++u) {
-              if (st0 + u < steps) {  // block-uniform
-                const int i = seg0 + (st0 + u) * kThreads + tid;
-                bool keep = false;
-                if (i < n_a && en[u].key >= key_lo) {
-                  const float p = __fdiv_rn(bits_f32(en[u].key), sum);
-                  keep = use_topk || p >= cutoff;
-                  en[u].key = f32_bits(p);
-                }
-                const unsigned kbal = __ballot_sync(0xffffffffu, keep);
-                if (keep) {
-                  listB[sm.u.compact.base[st0 + u] + sm.u.compact.cnt[st0 + u][warp] +
-                        __popc(kbal & ((1u << lane) - 1u))] = en[u];
-                }
-              }
-            }
-          }
-          n_b += seg_total;
-        }
-        __threadfence_block();
-        __syncthreads();
-        // sort by probability, descending; equal probabilities keep index order. The passes
-        // ping-pong between list B and free scratch (the tail of list A's buffer, or list A
-        // itself once it is no longer needed); after an even number of passes the result is
-        // back in list B.
-        if (n_b <= kRankSortMax) {
-          // small survivor set: rank every entry against all others. Composite key =
-          // (probability bits, inverted index): larger means earlier in the sorted order.
-          // kThreads / kRankSortMax threads share an entry, each scanning a part of the list.
-          const int ent = tid & (kRankSortMax - 1), part = tid / kRankSortMax;
-          Entry en;
-          en.key = 0;
-          en.idx = 0;
-          if (tid < n_b) {
-            en = listB[tid];
-            sm.u.rsort.ck[tid] = ((unsigned long long)en.key << 32) | (uint32_t)(0x7FFFFFFF - en.idx);
-            sm.u.rsort.rank[tid] = 0;
-          }
-          __syncthreads();
-          if (ent < n_b) {
-            const unsigned long long mine = sm.u.rsort.ck[ent];
-            constexpr int kParts = kThreads / kRankSortMax;
-            const int per = (n_b + kParts - 1) / kParts;
-            const int j0 = part * per, j1 = (j0 + per) < n_b ? (j0 + per) : n_b;
-            int rank = 0;
-#pragma unroll 8
-            for (int j = j0; j < j1; ++j) rank += sm.u.rsort.ck[j] > mine ? 1 : 0;
-            atomicAdd(&sm.u.rsort.rank[ent], rank);
-          }
-          __syncthreads();
-          if (tid < n_b) listB[sm.u.rsort.rank[tid]] = en;
-          __threadfence_block();
-        } else {
-          Entry* ping = listB;
-          Entry* pong = (n_a + n_b <= vocab) ? listA + n_a : listA;
-          for (int pass = 0; pass < 32 / kRadixBits; ++pass) {
-            radix_pass_desc(sm, ping, pong, n_b, pass * kRadixBits);
-            __threadfence_block();
-            Entry* t = ping;
-            ping = pong;
-            pong = t;
-          }
-        }
-        __syncthreads();
+        n_b = compact_candidates(sm, listA, n_a, listB, key_lo, sum, cutoff, use_topk);
+        sort_candidates(sm, listB, n_b, spare_is_list_a ? listA : listA + n_a);
         int pos;
         float hs, total;
         if (use_topk) {
           // the k most probable entries (fewer if fewer have e > 0); their float sum in
           // sorted order is topk_sum (sampler.cpp:105-108)
-          const int kk = topk < n_b ? topk : n_b;
-          list_search(sm, listB, n_b, kk, INFINITY, rp, &pos, &hs, &total);
-          have = true;
-          last_idx = kk - 1;
-          cum = total;
+          if (n_b >= topk || complete) {
+            const int kk = topk < n_b ? topk : n_b;
+            list_search(sm, listB, n_b, kk, INFINITY, rp, &pos, &hs, &total);
+            have = true;
+            last_idx = kk - 1;
+            cum = total;
+          } else {
+            n_a = gather_candidates(rm, sm, listA, exact_floor);
+            complete = true;
+          }
         } else if (list_search(sm, listB, n_b, n_b, topp, rp, &pos, &hs, &total)) {
           have = true;
           last_idx = pos;
           cum = hs;
-        } else if (bin_lo == 0) {
-          // complete candidate set and the sum never exceeded topp: keep everything
+        } else if (bin_lo == 0 && complete) {
+          // every candidate is in and the sum never exceeded topp: keep everything
           // (the "in case of rounding errors" branch, sampler.cpp:152)
           have = true;
           last_idx = n_b - 1;
           cum = total;
+        } else if (!complete) {
+          n_a = gather_candidates(rm, sm, listA, exact_floor);
+          complete = true;
         } else {
-          bin_lo = 0;  // the value threshold was too optimistic: take all candidates
+          take_all = true;  // the value threshold was too optimistic: take all candidates
         }
       }
-      if (n_b <= 0) {
+      if (n_b <= 0 || !have) {
         token = 0;  // no candidate at all (NaN rows): undefined in the reference
       } else {
         const float rr = __fmul_rn(coin, cum);  // sampler.cpp:162
@@ -1097,12 +1199,16 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
 // index order: the lowest index among equal maxima wins, -0 equals +0, a NaN never
 // replaces the running maximum, and a NaN in element 0 is never replaced.
 // ---------------------------------------------------------------------------------------
-constexpr int kArgChunk = 8;
+// Each thread keeps four 128-bit loads in flight per iteration: with one block per row and
+// fewer than two blocks per SM at batch 256, the bytes in flight decide the bandwidth.
+constexpr int kArgVecs = 4;
 
 template <typename T, bool kRawU16>
 __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
     int64_t* __restrict__ out_ids) {
+  constexpr int kPerVec = 16 / sizeof(T);
+  constexpr int kArgChunk = kArgVecs * kPerVec;  // consecutive logits per thread per iteration
   __shared__ float sv[kWarps];
   __shared__ int si[kWarps];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1114,30 +1220,47 @@ __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     for (int base = 0; base < vocab; base += kThreads * kArgChunk) {
       const int i0 = base + tid * kArgChunk;
       float x[kArgChunk];
-      if constexpr (kRawU16) {
-        // sample<uint16_t> compares the raw integers (exact in fp32)
+      if (vec_ok && i0 + kArgChunk <= vocab) {
+        uint4 raw[kArgVecs];
 #pragma unroll
-        for (int j = 0; j < kArgChunk; ++j) x[j] = (i0 + j < vocab) ? (float)row[i0 + j] : 0.0f;
-      } else {
-        constexpr int kPerVec = 16 / sizeof(T);
-        if (vec_ok && i0 + kArgChunk <= vocab) {
+        for (int q = 0; q < kArgVecs; ++q) raw[q] = __ldg(reinterpret_cast<const uint4*>(row + i0) + q);
 #pragma unroll
-          for (int q = 0; q < kArgChunk / kPerVec; ++q) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + i0) + q);
-            const T* p = reinterpret_cast<const T*>(&raw);
+        for (int q = 0; q < kArgVecs; ++q) {
+          const T* p = reinterpret_cast<const T*>(&raw[q]);
 #pragma unroll
-            for (int j = 0; j < kPerVec; ++j) x[q * kPerVec + j] = to_f32(p[j]);
+          for (int j = 0; j < kPerVec; ++j) {
+            if constexpr (kRawU16) {
+              x[q * kPerVec + j] = (float)p[j];  // sample<uint16_t> compares the raw integers
+            } else {
+              x[q * kPerVec + j] = to_f32(p[j]);
+            }
           }
-        } else {
+        }
+      } else {
 #pragma unroll
-          for (int j = 0; j < kArgChunk; ++j) x[j] = (i0 + j < vocab) ? to_f32(row[i0 + j]) : 0.0f;
+        for (int j = 0; j < kArgChunk; ++j) {
+          if constexpr (kRawU16) {
+            x[j] = (i0 + j < vocab) ? (float)row[i0 + j] : 0.0f;
+          } else {
+            x[j] = (i0 + j < vocab) ? to_f32(row[i0 + j]) : 0.0f;
+          }
         }
       }
+      if (i0 + kArgChunk <= vocab) {
 #pragma unroll
-      for (int j = 0; j < kArgChunk; ++j) {
-        if (i0 + j < vocab && x[j] > best) {
-          best = x[j];
-          besti = i0 + j;
+        for (int j = 0; j < kArgChunk; ++j) {
+          if (x[j] > best) {
+            best = x[j];
+            besti = i0 + j;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kArgChunk; ++j) {
+          if (i0 + j < vocab && x[j] > best) {
+            best = x[j];
+            besti = i0 + j;
+          }
         }
       }
     }
