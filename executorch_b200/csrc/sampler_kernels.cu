@@ -50,17 +50,19 @@ constexpr int kBinBase = kBinTop - (kBins - 1);
 constexpr int kRadixBits = 8;
 constexpr int kRadix = 1 << kRadixBits;
 constexpr int kFastSat = 1 << 25;           // per-thread clamp of chunk summaries
-constexpr int kCompactSteps = 448;          // list entries compacted per segment = 448 * kThreads
+constexpr int kCompactSteps = 224;          // list entries compacted per segment = 448 * kThreads
 constexpr float kGuessFloor = 1.0f / 8192.0f;  // first guess of a floor under the values that matter
 constexpr int kListBatch = 8;               // list entries a thread loads before using any of them
 constexpr int kRankSortMax = 512;           // survivor lists up to this size are rank-sorted in shared memory
 
-// bf16 table of e by logit bit pattern: both signs, |logit| in [2^-16, 2^8), plus +0 and -0.
-// Anything else (tiny, huge, infinite, NaN) is rare and computed directly.
-constexpr int kLutExpLo = 127 - 16;
-constexpr int kLutExpHi = 127 + 8;
-constexpr int kLutPerSign = (kLutExpHi - kLutExpLo) * 128;
-constexpr int kLutSize = 2 * kLutPerSign + 2;
+// bf16 table of e by logit bit pattern: both signs, |logit| in [2^-16, 2^16). Anything else
+// (zero, tiny, huge, infinite, NaN) is handled outside the table.
+// Addressing is pure bit-field work so that it can run on both halves of a packed pair:
+// adding kLutBias to a pattern moves the 32 covered exponents to 128..159, i.e. bits 14..12
+// of the biased pattern are 100 exactly for covered values, and the slot is its low 12 bits
+// (5 exponent bits, 7 mantissa bits) plus the sign as bit 12.
+constexpr uint32_t kLutBias = (128u - (127u - 16u)) << 7;  // 0x0880
+constexpr int kLutSize = 8192;
 
 struct Entry {
   uint32_t key;  // float bits of e_i (list A) or p_i (sorted lists); positive floats order like integers
@@ -90,7 +92,7 @@ struct __align__(16) Shared {
   int misc_i[4];
   float misc_f[4];
   union {
-    unsigned wbins[kWarps][kBins][2];  // per warp and value bin: count, sum of mantissa offsets
+    unsigned wbins[kWarps / 2][kBins][2];  // per warp pair and value bin: count, sum of mantissa offsets
     struct {
       unsigned short cnt[kCompactSteps][kWarps];  // survivors per (step, warp), then exclusive in step
       unsigned base[kCompactSteps];               // survivors in front of each step
@@ -399,20 +401,14 @@ struct RowMath {
 
   // bf16 bit pattern -> table slot, or -1 when the value is outside the table
   static __device__ __forceinline__ int lut_slot(uint32_t h) {
-    // selects only: sixteen of these run back to back and must not split the warp
-    const uint32_t a = h & 0x7FFFu;
-    const uint32_t sgn = h >> 15;
-    const uint32_t k = a - (uint32_t)(kLutExpLo << 7);
-    const int in_table = (int)(k + sgn * kLutPerSign);
-    const int zero = 2 * kLutPerSign + (int)sgn;
-    return k < (uint32_t)kLutPerSign ? in_table : (a == 0 ? zero : -1);
+    const uint32_t hb = h + kLutBias;
+    const int slot = (int)((hb & 0x0FFFu) | ((hb >> 3) & 0x1000u));
+    return (hb & 0x7000u) == 0x4000u ? slot : -1;
   }
 
   static __device__ __forceinline__ uint32_t lut_pattern(int slot) {
-    if (slot >= 2 * kLutPerSign) return (uint32_t)(slot - 2 * kLutPerSign) << 15;
-    const uint32_t sgn = slot >= kLutPerSign ? 1u : 0u;
-    const uint32_t k = (uint32_t)slot - sgn * kLutPerSign;
-    return (sgn << 15) | (k + (uint32_t)(kLutExpLo << 7));
+    const uint32_t hb = 0x4000u | ((uint32_t)slot & 0x0FFFu);
+    return ((hb - kLutBias) & 0x7FFFu) | (((uint32_t)slot & 0x1000u) << 3);
   }
 
   // Fills the table for this row (bf16 only): slot -> e, or e / S when probs is set.
@@ -451,19 +447,25 @@ struct RowMath {
   }
   __device__ __forceinline__ void eval_raw(const Raw& r, const S& sm, float (&e)[kChunk]) const {
     constexpr int kPerVec = 16 / sizeof(T);
-    int outside = 0;
-    (void)outside;
+    uint32_t all_and = 0xFFFFFFFFu, all_or = 0u;  // over the biased patterns of the chunk
+    (void)all_and;
+    (void)all_or;
 #pragma unroll
     for (int q = 0; q < kRawVecs; ++q) {
       if constexpr (S::kHasLut) {
         const uint32_t w[4] = {r.q[q].x, r.q[q].y, r.q[q].z, r.q[q].w};
+        const char* lut_bytes = reinterpret_cast<const char*>(sm.lut);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int s0 = lut_slot(w[j] & 0xFFFFu);
-          const int s1 = lut_slot(w[j] >> 16);
-          outside |= (s0 | s1);  // sign bit set if any pattern is outside the table
-          e[q * 8 + 2 * j] = sm.lut[s0 < 0 ? 0 : s0];
-          e[q * 8 + 2 * j + 1] = sm.lut[s1 < 0 ? 0 : s1];
+          // both halves at once. A carry out of the low half only happens for a low pattern
+          // that is outside the table anyway, and then the whole chunk is redone below.
+          const uint32_t wb = w[j] + (kLutBias | (kLutBias << 16));
+          all_and &= wb;
+          all_or |= wb;
+          const uint32_t off0 = ((wb << 2) & 0x3FFCu) | ((wb >> 1) & 0x4000u);
+          const uint32_t off1 = ((wb >> 14) & 0x3FFCu) | ((wb >> 17) & 0x4000u);
+          e[q * 8 + 2 * j] = *reinterpret_cast<const float*>(lut_bytes + off0);
+          e[q * 8 + 2 * j + 1] = *reinterpret_cast<const float*>(lut_bytes + off1);
         }
       } else {
         const T* p = reinterpret_cast<const T*>(&r.q[q]);
@@ -472,15 +474,17 @@ struct RowMath {
       }
     }
     if constexpr (S::kHasLut) {
-      if (outside < 0) {
-        // rare: a tiny, huge or non-finite logit in this chunk; redo those elements directly
+      // every pattern is inside the table iff bits 14..12 of every biased half are 100
+      if ((all_and & 0x40004000u) != 0x40004000u || (all_or & 0x30003000u) != 0u) {
+        // rare: a zero, tiny, huge or non-finite logit in this chunk; redo the chunk element by
+        // element (table where possible, direct evaluation otherwise)
 #pragma unroll
         for (int q = 0; q < kRawVecs; ++q) {
           const uint32_t w[4] = {r.q[q].x, r.q[q].y, r.q[q].z, r.q[q].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            if (lut_slot(w[j] & 0xFFFFu) < 0) e[q * 8 + 2 * j] = direct(bits_f32((w[j] & 0xFFFFu) << 16), sm);
-            if (lut_slot(w[j] >> 16) < 0) e[q * 8 + 2 * j + 1] = direct(bits_f32(w[j] & 0xFFFF0000u), sm);
+            e[q * 8 + 2 * j] = from_pattern(w[j] & 0xFFFFu, sm);
+            e[q * 8 + 2 * j + 1] = from_pattern(w[j] >> 16, sm);
           }
         }
       }
@@ -669,7 +673,7 @@ __device__ bool pick_value_threshold(
   const int tid = threadIdx.x, warp = tid >> 5;
   __syncthreads();  // earlier users of the union are done
   // per-warp integer counters, filled by one coalesced pass over the list
-  for (int b = tid; b < kWarps * kBins * 2; b += kThreads) (&sm.u.wbins[0][0][0])[b] = 0;
+  for (int b = tid; b < (kWarps / 2) * kBins * 2; b += kThreads) (&sm.u.wbins[0][0][0])[b] = 0;
   __syncthreads();
   for (int i0 = 0; i0 < n_a; i0 += kListBatch * kThreads) {
     uint32_t k[kListBatch];
@@ -683,8 +687,8 @@ __device__ bool pick_value_threshold(
       if (i0 + u * kThreads + tid < n_a) {
         int bin = (int)(k[u] >> kBinShift) - kBinBase;
         bin = bin < 0 ? 0 : (bin < kBins ? bin : kBins - 1);
-        atomicAdd(&sm.u.wbins[warp][bin][0], 1u);
-        atomicAdd(&sm.u.wbins[warp][bin][1], (k[u] >> 8) & 0x1FFFu);
+        atomicAdd(&sm.u.wbins[warp >> 1][bin][0], 1u);
+        atomicAdd(&sm.u.wbins[warp >> 1][bin][1], (k[u] >> 8) & 0x1FFFu);
       }
     }
   }
@@ -696,7 +700,7 @@ __device__ bool pick_value_threshold(
   if (tid < kBins) {
     unsigned c = 0, o = 0;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
+    for (int w = 0; w < kWarps / 2; ++w) {
       c += sm.u.wbins[w][tid][0];
       o += sm.u.wbins[w][tid][1];
     }
