@@ -77,9 +77,9 @@ struct __align__(16) Shared {
   float lut[kLut ? kLutSize : 2];
   alignas(16) float head[kHead];  // read as float4
   SeqSummary wsum[kWarps];
-  int wsum_i[2][kWarps];  // slots used by alternate scan rounds (see seqsum_tile)
+  int wsum_i[3][kWarps];  // slots used by successive scan rounds in rotation (see seqsum_tile)
   int first[2];
-  int two_parity[2];
+  int two_parity[3];
   int wcnt[2][kWarps];
   float redf[kWarps];
   int redi[kWarps];
@@ -160,10 +160,12 @@ __device__ __forceinline__ int block_excl_count(S& sm, int cnt, int* total) {
 // block scan is a plain integer prefix sum. A tie anywhere switches the round to the
 // two-parity summaries of exact_math.cuh (one more barrier).
 //
-// Rounds alternate between two sets of shared slots (`rp`, block-uniform, carried by the
-// caller across tiles), so a round needs no barrier to protect its slots from the readers
-// of the previous round: two barriers per round, a third only when a chunk has to be
-// redone. Invariant at round entry: first[rp] == kThreads and two_parity[rp] == 0.
+// Rounds rotate through three sets of shared slots (`rp`, block-uniform, carried by the
+// caller across tiles), so a round needs no barrier to protect its slots from the previous
+// round. A round costs ONE barrier when no chunk leaves the binade: once the warp totals
+// are visible, every warp works out redundantly which warp (if any) holds the first chunk to
+// redo. Only then does that warp redo the chunk and publish the new sum behind a second
+// barrier. Invariant at round entry: two_parity[rp] == 0.
 //
 // With kSearch, also looks for the first term after which the running sum exceeds `thr`
 // (terms at position >= limit, counted from pos0 of thread 0's first term, must be zero
@@ -215,8 +217,11 @@ __device__ __forceinline__ bool seqsum_tile(
       if (lane >= d) inc += o;
     }
     if (lane == 31) sm.wsum_i[rp][warp] = inc < kFastSat ? inc : kFastSat;
-    __syncthreads();  // ---- barrier 1
-    int n_in, n_out, n_total;
+    __syncthreads();  // ---- barrier 1: warp totals (and the two-parity flag) are visible
+    const int next_rp = rp == 2 ? 0 : rp + 1;
+    if (tid == 0) sm.two_parity[next_rp == 2 ? 0 : next_rp + 1] = 0;  // slot of the round after next
+    int n_in, n_out;       // N in front of / behind this thread's chunk
+    int n_wend;            // N behind the warp `lane` (lanes < kWarps), for the warp-level decision
     if (!sm.two_parity[rp]) {
       int wt = (lane < kWarps) ? sm.wsum_i[rp][lane] : 0;
 #pragma unroll
@@ -226,7 +231,7 @@ __device__ __forceinline__ bool seqsum_tile(
       }
       int pre = __shfl_sync(0xffffffffu, wt, warp > 0 ? warp - 1 : 0);
       if (warp == 0) pre = 0;
-      n_total = n_s + __shfl_sync(0xffffffffu, wt, kWarps - 1);
+      n_wend = n_s + wt;
       n_in = n_s + pre + (inc - mine.a0);
       n_out = n_in + mine.a0;
     } else {
@@ -255,66 +260,73 @@ __device__ __forceinline__ bool seqsum_tile(
         o.a1 = __shfl_up_sync(0xffffffffu, wt.a1, d);
         if (lane >= d) wt = seq_compose(o, wt);
       }
-      SeqSummary pre, total;
+      SeqSummary pre;
       pre.a0 = __shfl_sync(0xffffffffu, wt.a0, warp > 0 ? warp - 1 : 0);
       pre.a1 = __shfl_sync(0xffffffffu, wt.a1, warp > 0 ? warp - 1 : 0);
       if (warp == 0) seq_identity(&pre);
-      total.a0 = __shfl_sync(0xffffffffu, wt.a0, kWarps - 1);
-      total.a1 = __shfl_sync(0xffffffffu, wt.a1, kWarps - 1);
+      n_wend = seq_apply(n_s, wt);
       pre = seq_compose(pre, excl);
       n_in = seq_apply(n_s, pre);
       n_out = seq_apply(n_in, mine);
-      n_total = seq_apply(n_s, total);
     }
-    bool flag = active && (n_out >= kSeqLimit);
+    // Which warp holds the first chunk to redo: the first whose end value left the binade
+    // (N >= 2^24) or, when searching, exceeds thr. N only grows along the tile, so this is
+    // decided from the warp-end values alone, identically by every warp.
+    bool wflag = lane < kWarps && n_wend >= kSeqLimit;
     if (kSearch) {
-      if (active && n_out < kSeqLimit && seq_value(kb, n_out) > thr) flag = true;
+      if (lane < kWarps && n_wend < kSeqLimit && seq_value(kb, n_wend) > thr) wflag = true;
     }
-    const unsigned ballot = __ballot_sync(0xffffffffu, flag);
-    if (ballot != 0 && lane == 0) atomicMin(&sm.first[rp], warp * 32 + __ffs(ballot) - 1);
-    if (tid == 0) {
-      // prepare the other slot set for the next round; its last readers are behind barrier 1
-      sm.first[rp ^ 1] = kThreads;
-      sm.two_parity[rp ^ 1] = 0;
-      sm.hit_found = 0;
-    }
-    __syncthreads();  // ---- barrier 2
-    const int first = sm.first[rp];
-    rp ^= 1;
-    if (first == kThreads) {
+    const unsigned wb = __ballot_sync(0xffffffffu, wflag);
+    rp = next_rp;
+    if (wb == 0) {
       // nothing left the binade: the whole tile is summarised exactly
-      s = seq_value(kb, n_total);
+      s = seq_value(kb, __shfl_sync(0xffffffffu, n_wend, kWarps - 1));
       return false;
     }
-    if (tid == first) {
-      // The sum in front of this chunk is exact; redo the chunk with real float additions
-      // (it leaves the binade here, or it contains the searched position).
-      float acc = seq_value(kb, n_in);
-      bool found = false;
+    const int redo_warp = __ffs(wb) - 1;
+    if (warp == redo_warp) {
+      bool flag = active && (n_out >= kSeqLimit);
+      if (kSearch) {
+        if (active && n_out < kSeqLimit && seq_value(kb, n_out) > thr) flag = true;
+      }
+      const unsigned lb = __ballot_sync(0xffffffffu, flag);
+      const int first_lane = __ffs(lb) - 1;  // exists: this warp's end value is flagged
+      if (lane == first_lane) {
+        // The sum in front of this chunk is exact; redo the chunk with real float additions
+        // (it leaves the binade here, or it contains the searched position).
+        float acc = seq_value(kb, n_in);
+        int found = 0;
 #pragma unroll
-      for (int j = 0; j < kChunk; ++j) {
-        acc = __fadd_rn(acc, v[j]);
-        if (kSearch) {
-          const int pos = pos0 + tid * kChunk + j;
-          if (!found && acc > thr && pos < limit) {
-            found = true;
-            sm.hit_found = 1;
-            sm.hit_idx = pos;
-            sm.hit_val = acc;
+        for (int j = 0; j < kChunk; ++j) {
+          acc = __fadd_rn(acc, v[j]);
+          if (kSearch) {
+            const int pos = pos0 + tid * kChunk + j;
+            if (!found && acc > thr && pos < limit) {
+              found = 1;
+              sm.hit_idx = pos;
+              sm.hit_val = acc;
+            }
           }
         }
+        sm.hit_found = found;
+        sm.s_bcast = acc;
+        sm.first[0] = tid;
       }
-      sm.s_bcast = acc;
     }
-    __syncthreads();  // ---- barrier 3 (only in rounds that redo a chunk)
+    __syncthreads();  // ---- barrier 2 (only in rounds that redo a chunk)
     s = sm.s_bcast;
-    if (kSearch && sm.hit_found) {
+    const int first = sm.first[0];
+    const bool hit = kSearch && sm.hit_found;
+    if (hit) {
       *hit_pos = sm.hit_idx;
       *hit_sum = sm.hit_val;
-      return true;
     }
     consumed = first + 1;
-    if (consumed >= kThreads) return false;
+    if (hit || consumed >= kThreads) {
+      __syncthreads();  // the result slots may be rewritten by the caller's next step
+      return hit;
+    }
+    // the next round's barrier 1 orders these reads before the next writes of the slots
   }
 }
 
@@ -930,10 +942,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   __shared__ S sm;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
-  if (tid < 2) {
-    sm.first[tid] = kThreads;
-    sm.two_parity[tid] = 0;
-  }
+  if (tid < 3) sm.two_parity[tid] = 0;
   int rp = 0;  // which set of scan-round slots the next round uses (see seqsum_tile)
   // Guessed floor under the values that matter (nucleus members / the k largest). Pass 2 lists
   // only e >= guess; if that turns out to be too high for a row, the row is regathered with
@@ -1043,10 +1052,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       const float floor_now = use_topp ? fmaxf(e_floor, cutoff * s * 0.999999f) : e_floor;
       (void)exact_floor0;
       int cnt = 0, inc = 0;
+      unsigned cmask = 0;  // bit j: e[j] is a candidate
       if (use_list) {
         // entries beyond the row are 0 and the floor is > 0, so they never count
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) cnt += (e[j] >= floor_now) ? 1 : 0;
+        for (int j = 0; j < kChunk; ++j) cmask |= (e[j] >= floor_now) ? (1u << j) : 0u;
+        cnt = __popc(cmask);
         inc = cnt;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -1059,18 +1070,18 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       float hs;
       seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
       if (use_list) {
-        int pre = 0, tot = 0;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-          const int c = sm.wcnt[buf][w];
-          if (w < warp) pre += c;
-          tot += c;
-        }
+        // candidates of the warps in front of this one, and of the whole tile
+        const int wc = lane < kWarps ? sm.wcnt[buf][lane] : 0;
+        const int pre = __reduce_add_sync(0xffffffffu, lane < warp ? wc : 0);
+        const int tot = __reduce_add_sync(0xffffffffu, wc);
         int off = n_a + pre + inc - cnt;
-        if (cnt > 0) {
+        // Candidates are rare (well under 1 % of the logits): visit only the positions j at
+        // which some lane of the warp has one.
+        const unsigned any = __reduce_or_sync(0xffffffffu, cmask);
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) {
-            if (e[j] >= floor_now) {
+        for (int j = 0; j < kChunk; ++j) {
+          if (any & (1u << j)) {  // warp-uniform
+            if (cmask & (1u << j)) {
               Entry en;
               en.key = f32_bits(e[j]);
               en.idx = i0 + j;
