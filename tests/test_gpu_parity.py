@@ -260,6 +260,46 @@ def test_degenerate_distributions(cuda_device, restatement):
         assert np.array_equal(gpu_sample(xb, "bf16", 1.0, 0.9, seeds, cuda_device), want), name
 
 
+def test_mixed_batch_larger_than_the_grid(cuda_device, restatement):
+    """More rows than resident blocks, so every block samples several rows in turn and carries
+    its candidate-floor guess from one row to the next; peaked, Zipf-shaped, flat and one-hot
+    rows alternate so that the guess is wrong in both directions."""
+    rng = np.random.default_rng(21)
+    vocab, rows = 6000, 900
+    x = np.empty((rows, vocab), dtype=np.float32)
+    for r in range(rows):
+        kind = r % 4
+        if kind == 0:
+            x[r] = -1.3 * np.log(1.0 + rng.permutation(vocab)) + 0.5 * rng.standard_normal(vocab)
+        elif kind == 1:
+            x[r] = 0.05 * rng.standard_normal(vocab)
+        elif kind == 2:
+            x[r] = rng.standard_normal(vocab)
+            x[r, rng.integers(vocab)] = 25.0
+        else:
+            x[r] = 3.0 * rng.standard_normal(vocab)
+    seeds = rng.integers(0, 2**62, size=rows).astype(np.uint64)
+    for dtype in ("fp32", "bf16"):
+        xd = x if dtype == "fp32" else W.f32_to_bf16_bits(x)
+        for t, p, k in ((0.8, 0.9, 0), (1.0, 0.3, 0), (0.7, 0.99, 0), (0.9, 0.9, 25), (0.9, 0.9, 3000)):
+            want = restatement.sample_rows(xd, t, p, seeds, dtype=dtype, topk=k, threads=8)
+            got = gpu_sample(xd, dtype, t, p, seeds, cuda_device, topk=k)
+            assert np.array_equal(got, want), (dtype, t, p, k, np.nonzero(got != want)[0][:8])
+
+
+def test_vocabulary_beyond_one_compaction_segment(cuda_device, restatement):
+    """A flat row of 300 000 fp16 logits: the nucleus holds ~270 000 tokens, so the candidate
+    list spans several compaction segments and goes through the radix sort."""
+    rng = np.random.default_rng(22)
+    vocab = 300_000
+    x = (0.05 * rng.standard_normal((2, vocab))).astype(np.float16).view(np.uint16)
+    seeds = np.array([4, 5], dtype=np.uint64)
+    for t, p, k in ((1.0, 0.9, 0), (1.0, 1.0, 0), (1.0, 0.9, 150_000)):
+        want = restatement.sample_rows(x, t, p, seeds, dtype="fp16", topk=k)
+        got = gpu_sample(x, "fp16", t, p, seeds, cuda_device, topk=k)
+        assert np.array_equal(got, want), (t, p, k)
+
+
 def test_mode_selection_setters_and_errors(cuda_device, restatement):
     x = W.rows_numpy("c1", [3, 4, 5], vocab=2048)
     t = torch.from_numpy(x).to(cuda_device)
