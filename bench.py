@@ -176,6 +176,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: ids stored into the peers' buffers by the kernel (p2p) or all-gathered (nccl)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -214,10 +216,30 @@ def main():
     all_ids = torch.empty(total_rows, dtype=torch.int64, device=dev) if world > 1 else local_ids
     sampler = Sampler(vocab, cfg.temperature, cfg.topp, 0, device=dev)
 
+    exchange, exchange_name = None, "none"
+    if world > 1:
+        exchange_name = "all_gather of int64 ids (NCCL)"
+        if args.exchange == "p2p":
+            try:
+                from executorch_b200.sharded import PeerIdExchange
+                exchange = PeerIdExchange(total_rows, dev)
+                exchange_name = "ids stored into every peer's buffer by the kernel epilogue + symmetric-memory barrier"
+            except Exception as exc:  # symmetric memory unavailable: use the collective
+                exchange_name += f" (peer buffers unavailable: {type(exc).__name__})"
+        # every rank must take the same path
+        flag = torch.tensor([1 if exchange is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag) == 0:
+            exchange = None
+
     def step(i):
-        sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
-        if world > 1:
-            dist.all_gather_into_tensor(all_ids, local_ids)
+        if exchange is not None:
+            sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
+            exchange.finish()
+        else:
+            sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
+            if world > 1:
+                dist.all_gather_into_tensor(all_ids, local_ids)
 
     for i in range(warmup):
         states.copy_(states0)
@@ -239,10 +261,15 @@ def main():
     t0.record()
     for i in range(args.steps):
         k_start[i].record()
-        sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
-        k_end[i].record()
-        if world > 1:
-            dist.all_gather_into_tensor(all_ids, local_ids)
+        if exchange is not None:
+            sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
+            k_end[i].record()
+            exchange.finish()
+        else:
+            sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
+            k_end[i].record()
+            if world > 1:
+                dist.all_gather_into_tensor(all_ids, local_ids)
     t1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -291,7 +318,7 @@ def main():
                 "workload": "c3: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0.7, top-p 0.95, seed=row",
                 "rows_per_gpu": rows, "vocab": vocab, "global_rows": total_rows,
                 "l2": f"{NBUF} rotating input batches ({NBUF * rows * vocab * 2 / 1e6:.0f} MB > 126 MB L2)",
-                "exchange": "all_gather of int64 ids (NCCL)" if world > 1 else "none",
+                "exchange": exchange_name,
             },
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,

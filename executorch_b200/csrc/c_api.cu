@@ -172,12 +172,13 @@ etb200_error_t ensure_scratch(etb200_sampler* h, int blocks) {
 // Shared by the device- and host-buffer entry points. All pointers are device pointers.
 etb200_error_t sample_rows_device(
     etb200_sampler* h, const void* logits, int dtype, int64_t rows, int64_t row_stride,
-    unsigned long long* rng_states, int64_t* out_ids, cudaStream_t stream) {
+    unsigned long long* rng_states, int64_t* out_ids, cudaStream_t stream,
+    const PeerOut& peers = PeerOut{}) {
   if (rows == 0) return ETB200_OK;
   if (h->inv_temperature == 0.0f) {
     // greedy: no coin is drawn and the RNG state does not move (sampler.cpp:226-228)
     const int blocks = (int)(rows < (int64_t)h->sm_count * 4 ? rows : (int64_t)h->sm_count * 4);
-    ETB_CUDA(launch_argmax_rows(dtype, logits, rows, h->vocab, row_stride, out_ids, blocks, stream));
+    ETB_CUDA(launch_argmax_rows(dtype, logits, rows, h->vocab, row_stride, out_ids, peers, blocks, stream));
     h->launches += 1;
     return ETB200_OK;
   }
@@ -199,7 +200,7 @@ etb200_error_t sample_rows_device(
   }
   ETB_CUDA(launch_sample_rows(
       dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk, rng_states,
-      out_ids, h->scratch, blocks, h->table, h->d_status, stream));
+      out_ids, peers, h->scratch, blocks, h->table, h->d_status, stream));
   h->launches += 1;
   return ETB200_OK;
 }
@@ -307,6 +308,29 @@ etb200_error_t etb200_sampler_sample_rows(
       h, logits_device, dtype, rows, row_stride_elems,
       reinterpret_cast<unsigned long long*>(rng_states_device), out_ids_device,
       static_cast<cudaStream_t>(stream));
+}
+
+etb200_error_t etb200_sampler_sample_rows_scatter(
+    etb200_sampler_t* h, const void* logits_device, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,
+    int32_t n_dest, int64_t dest_offset, void* stream) {
+  ETB_CHECK_ARG(dest_buffers != nullptr, "dest_buffers is null");
+  ETB_CHECK_ARG(n_dest >= 1 && n_dest <= kMaxPeers, "n_dest must be in [1, %d], got %d", kMaxPeers, n_dest);
+  ETB_CHECK_ARG(dest_offset >= 0, "dest_offset must be >= 0");
+  PeerOut peers{};
+  for (int i = 0; i < n_dest; ++i) {
+    ETB_CHECK_ARG(dest_buffers[i] != nullptr, "dest_buffers[%d] is null", i);
+    peers.ptr[i] = dest_buffers[i];
+  }
+  peers.n = n_dest;
+  peers.offset = dest_offset;
+  etb200_error_t err = check_common(h, logits_device, dtype, rows, row_stride_elems, dest_buffers[0]);
+  if (err != ETB200_OK) return err;
+  DeviceGuard guard(h->device);
+  return sample_rows_device(
+      h, logits_device, dtype, rows, row_stride_elems,
+      reinterpret_cast<unsigned long long*>(rng_states_device), nullptr,
+      static_cast<cudaStream_t>(stream), peers);
 }
 
 etb200_error_t etb200_sampler_sample_rows_host(

@@ -381,6 +381,18 @@ __device__ __forceinline__ bool head_sum(
   return hit;
 }
 
+// Writes the token of row r: to out_ids[r], or -- when peer buffers are given -- straight into
+// every listed buffer at [offset + r] (each may live on another GPU of the node: plain
+// stores over NVLink, one thread per destination). Block-uniform `token`.
+__device__ __forceinline__ void store_token(
+    int64_t* __restrict__ out_ids, const PeerOut& peers, int64_t r, int token) {
+  if (peers.n == 0) {
+    if (threadIdx.x == 0) out_ids[r] = (int64_t)token;
+  } else if ((int)threadIdx.x < peers.n) {
+    peers.ptr[threadIdx.x][peers.offset + r] = (int64_t)token;
+  }
+}
+
 // xorshift64* step and 24-bit coin of the reference (sampler.cpp:210-220).
 __device__ __forceinline__ float next_coin(unsigned long long* state) {
   unsigned long long s = *state;
@@ -936,7 +948,8 @@ template <typename T, bool kLut>
 __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
     float topp, int topk, unsigned long long* __restrict__ rng_states,
-    int64_t* __restrict__ out_ids, Entry* scratch, ExpTable table, int* __restrict__ status) {
+    int64_t* __restrict__ out_ids, PeerOut peers, Entry* scratch, ExpTable table,
+    int* __restrict__ status) {
   (void)status;
   using S = Shared<kLut>;
   __shared__ S sm;
@@ -1204,7 +1217,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         token = listB[j].idx;
       }
     }
-    if (tid == 0) out_ids[r] = (int64_t)token;
+    store_token(out_ids, peers, r, token);
     __syncthreads();
   }
 }
@@ -1221,7 +1234,7 @@ constexpr int kArgVecs = 4;
 template <typename T, bool kRawU16>
 __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
-    int64_t* __restrict__ out_ids) {
+    int64_t* __restrict__ out_ids, PeerOut peers) {
   constexpr int kPerVec = 16 / sizeof(T);
   constexpr int kArgChunk = kArgVecs * kPerVec;  // consecutive logits per thread per iteration
   __shared__ float sv[kWarps];
@@ -1317,8 +1330,10 @@ __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
       } else if (besti == 0x7fffffff) {
         ans = 0;
       }
-      out_ids[r] = (int64_t)ans;
+      sv[0] = __int_as_float(ans);
     }
+    __syncthreads();
+    store_token(out_ids, peers, r, __float_as_int(sv[0]));
   }
 }
 
@@ -1353,29 +1368,30 @@ int sampler_threads() { return kThreads; }
 template <typename T, bool kLut>
 static cudaError_t launch_sample_t(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
-    int topk, unsigned long long* rng_states, int64_t* out_ids, void* scratch, int blocks,
-    const ExpTable& table, int* status, cudaStream_t stream) {
+    int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, void* scratch,
+    int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
   sample_rows_kernel<T, kLut><<<blocks, kThreads, 0, stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
+      peers,
       static_cast<Entry*>(scratch), table, status);
   return cudaGetLastError();
 }
 
 cudaError_t launch_sample_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
-    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, void* scratch,
-    int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
+    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers,
+    void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
   switch (dtype) {
     case kDtypeFloat:
       return launch_sample_t<float, false>(logits, rows, vocab, row_stride, inv_t, topp, topk,
-                                           rng_states, out_ids, scratch, blocks, table, status, stream);
+                                           rng_states, out_ids, peers, scratch, blocks, table, status, stream);
     case kDtypeHalf:
       return launch_sample_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp, topk,
-                                            rng_states, out_ids, scratch, blocks, table, status,
+                                            rng_states, out_ids, peers, scratch, blocks, table, status,
                                             stream);
     case kDtypeBFloat16:
       return launch_sample_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp, topk,
-                                                  rng_states, out_ids, scratch, blocks, table,
+                                                  rng_states, out_ids, peers, scratch, blocks, table,
                                                   status, stream);
     default:
       return cudaErrorInvalidValue;
@@ -1384,23 +1400,23 @@ cudaError_t launch_sample_rows(
 
 cudaError_t launch_argmax_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
-    int blocks, cudaStream_t stream) {
+    const PeerOut& peers, int blocks, cudaStream_t stream) {
   switch (dtype) {
     case kDtypeFloat:
       argmax_rows_kernel<float, false><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const float*>(logits), rows, vocab, row_stride, out_ids);
+          static_cast<const float*>(logits), rows, vocab, row_stride, out_ids, peers);
       break;
     case kDtypeHalf:
       argmax_rows_kernel<__half, false><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const __half*>(logits), rows, vocab, row_stride, out_ids);
+          static_cast<const __half*>(logits), rows, vocab, row_stride, out_ids, peers);
       break;
     case kDtypeBFloat16:
       argmax_rows_kernel<__nv_bfloat16, false><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, out_ids);
+          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, out_ids, peers);
       break;
     case kDtypeUInt16:
       argmax_rows_kernel<unsigned short, true><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const unsigned short*>(logits), rows, vocab, row_stride, out_ids);
+          static_cast<const unsigned short*>(logits), rows, vocab, row_stride, out_ids, peers);
       break;
     default:
       return cudaErrorInvalidValue;

@@ -17,6 +17,16 @@ constexpr int kDtypeFloat = 6;
 constexpr int kDtypeBFloat16 = 15;
 constexpr int kDtypeUInt16 = 27;
 
+// Optional destinations of the sampled ids: up to kMaxPeers int64 buffers (this GPU's and its
+// peers' -- pointers obtained from symmetric / peer-mapped memory), each written at
+// [offset + row]. n == 0 means "write out_ids[row] only".
+constexpr int kMaxPeers = 16;
+struct PeerOut {
+  int64_t* ptr[kMaxPeers];
+  int n;
+  long long offset;
+};
+
 // Bytes of candidate-list scratch the sampling kernel needs when launched with `blocks`
 // thread blocks on rows of `vocab` logits.
 size_t sampler_scratch_bytes(int vocab, int blocks);
@@ -31,13 +41,13 @@ int sampler_threads();
 // token. Top-k and top-p need `scratch` (sampler_scratch_bytes).
 cudaError_t launch_sample_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
-    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, void* scratch,
-    int blocks, const ExpTable& table, int* status, cudaStream_t stream);
+    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers,
+    void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream);
 
 // temperature == 0: greedy argmax of every row.
 cudaError_t launch_argmax_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
-    int blocks, cudaStream_t stream);
+    const PeerOut& peers, int blocks, cudaStream_t stream);
 
 // y[i] = expf_ref(x[i]) on the device, for x <= 0: lets a test compare the device
 // exponential with the host libm.

@@ -107,7 +107,7 @@ etb200_error_t etb200_sample_rows_static(
   if (inv_t == 0.0f) {
     const int64_t cap = (int64_t)sms * 4;
     e = launch_argmax_rows(dtype, logits_device, rows, vocab_size, row_stride_elems, out_ids_device,
-                           (int)(rows < cap ? rows : cap), st);
+                           PeerOut{}, (int)(rows < cap ? rows : cap), st);
   } else {
     if (dtype == kDtypeUInt16)
       return fail(ETB200_NOT_SUPPORTED, "UInt16 logits can only be sampled at temperature 0");
@@ -121,7 +121,7 @@ etb200_error_t etb200_sample_rows_static(
     make_exp_table(&table);
     e = launch_sample_rows(dtype, logits_device, rows, vocab_size, row_stride_elems, inv_t, topp,
                            /*topk=*/0, reinterpret_cast<unsigned long long*>(rng_states_device), out_ids_device,
-                           scratch, (int)blocks, table, nullptr, st);
+                           PeerOut{}, scratch, (int)blocks, table, nullptr, st);
   }
   if (e != cudaSuccess) return fail(ETB200_INTERNAL, cudaGetErrorString(e));
   return ETB200_OK;

@@ -144,6 +144,24 @@ class Sampler:
             states_ptr, C.c_void_p(out.data_ptr()), self._stream()))
         return out
 
+    def sample_rows_scatter(self, logits: torch.Tensor, rng_states: torch.Tensor | None,
+                            dest_ptrs, dest_offset: int) -> None:
+        """Like ``sample_rows``, but the id of row r is stored into every int64 buffer of
+        ``dest_ptrs`` (device addresses, this GPU's and its peers') at index ``dest_offset + r``.
+        Asynchronous; the caller synchronises the ranks afterwards."""
+        self._check_rows(logits)
+        rows = logits.shape[0]
+        states_ptr = C.c_void_p(0)
+        if rng_states is not None:
+            if (rng_states.dtype != torch.int64 or rng_states.numel() != rows
+                    or not rng_states.is_contiguous() or rng_states.device != self.device):
+                raise ValueError("rng_states must be a contiguous int64 device tensor, one per row")
+            states_ptr = C.c_void_p(rng_states.data_ptr())
+        arr = (C.c_void_p * len(dest_ptrs))(*[C.c_void_p(int(p)) for p in dest_ptrs])
+        _lib.check(_lib.load().etb200_sampler_sample_rows_scatter(
+            self._h, C.c_void_p(logits.data_ptr()), _dtype_code(logits), rows, logits.stride(0),
+            states_ptr, arr, len(dest_ptrs), dest_offset, self._stream()))
+
     def sample_rows_host(self, logits, rng_states: np.ndarray | None, dtype: str | None = None
                          ) -> np.ndarray:
         """Host-memory entry: ``logits`` is a [rows, vocab] CPU tensor or numpy array

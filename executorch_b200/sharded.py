@@ -20,6 +20,29 @@ def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
     return start, base + (1 if rank < extra else 0)
 
 
+class PeerIdExchange:
+    """The id exchange without a collective call: one int64 buffer of ``total_rows`` per rank in
+    torch's symmetric memory (every rank can address every peer's copy over NVLink). The
+    sampling kernel's epilogue stores each id into all copies
+    (``Sampler.sample_rows_scatter``); ``finish()`` enqueues the barrier after which this
+    rank's copy holds the ids of all ranks. Ranks must be the GPUs of one node."""
+
+    def __init__(self, total_rows: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.buffer = symm_mem.empty(total_rows, dtype=torch.int64, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.dest_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.dest_ptrs) > 16:
+            raise ValueError("at most 16 ranks can exchange ids through peer buffers")
+
+    def finish(self) -> torch.Tensor:
+        # all ranks' stores are ordered before the barrier's release on each stream
+        self.handle.barrier(channel=0)
+        return self.buffer
+
+
 class ShardedSampler:
     """Samples this rank's rows with ``local_sample`` and gathers all ids on every rank.
 
@@ -27,7 +50,10 @@ class ShardedSampler:
     tests inject a CPU stand-in to exercise the exchange with the gloo backend."""
 
     def __init__(self, local_sample: Callable[[torch.Tensor, torch.Tensor | None], torch.Tensor],
-                 total_rows: int, group=None):
+                 total_rows: int, group=None, scatter=None, device=None):
+        """``scatter(logits, rng_states, dest_ptrs, dest_offset)`` (normally
+        ``Sampler.sample_rows_scatter``) selects the peer-buffer exchange instead of the
+        all-gather; it needs equal shards and a CUDA ``device``."""
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.local_sample = local_sample
@@ -37,11 +63,20 @@ class ShardedSampler:
         self.total_rows = total_rows
         self.start, self.count = shard_rows(total_rows, self.rank, self.world)
         self.even = total_rows % self.world == 0
+        self.scatter = scatter
+        self.exchange = None
+        if scatter is not None:
+            if not self.even:
+                raise ValueError("the peer-buffer exchange needs equal shards")
+            self.exchange = PeerIdExchange(total_rows, device, group)
 
     def sample_rows(self, local_logits: torch.Tensor, local_states: torch.Tensor | None,
                     out: torch.Tensor | None = None) -> torch.Tensor:
         if local_logits.shape[0] != self.count:
             raise ValueError(f"rank {self.rank} owns {self.count} rows, got {local_logits.shape[0]}")
+        if self.exchange is not None:
+            self.scatter(local_logits, local_states, self.exchange.dest_ptrs, self.start)
+            return self.exchange.finish()
         ids = self.local_sample(local_logits, local_states)
         if out is None:
             out = torch.empty(self.total_rows, dtype=torch.int64, device=ids.device)

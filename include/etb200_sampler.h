@@ -117,6 +117,18 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows(
     int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* out_ids_device,
     void* stream);
 
+/* Multi-GPU form of etb200_sampler_sample_rows (no counterpart in the reference, which is
+ * single-device): instead of one out_ids array, the kernel's epilogue stores the id of row r
+ * into EVERY buffer dest_buffers[0..n_dest) at index dest_offset + r. The buffers are int64
+ * device arrays that this process can address: its own and its peers' (symmetric / peer-mapped
+ * memory of the GPUs of one node), so that after a barrier among the ranks every GPU holds
+ * all ids without a separate all-gather. dest_buffers is a HOST array of n_dest (<= 16) device
+ * pointers. Asynchronous on `stream`; the caller provides the cross-GPU barrier. */
+ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_scatter(
+    etb200_sampler_t* handle, const void* logits_device, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,
+    int32_t n_dest, int64_t dest_offset, void* stream);
+
 /* Same as etb200_sampler_sample_rows for callers whose logits live in HOST memory (what
  * sample_from_logits receives from a CPU tensor, util.h:25-55): copies the rows to the
  * device, samples, copies ids and advanced states back, and synchronises the stream.

@@ -1,0 +1,66 @@
+"""Row sharding across the GPUs of one node, with real samplers: both id exchanges (NCCL
+all-gather, and ids stored into the peers' buffers by the kernel epilogue) must leave every
+rank with the tokens a single GPU would produce. Runs only where at least two GPUs are
+visible; ranks leave together, between steps."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import oracle
+        from executorch_b200 import Sampler, seeds_to_states
+        from executorch_b200 import workloads as W
+        from executorch_b200.sharded import ShardedSampler
+
+        vocab, total = 20000, 16 * world
+        x = W.rows_numpy("c3", list(range(total)), vocab=vocab)
+        seeds = np.arange(total, dtype=np.uint64) + 3
+        want = oracle.Restatement().sample_rows(x, 0.7, 0.9, seeds, dtype="bf16", threads=2)
+        s = Sampler(vocab, 0.7, 0.9, 0, device=dev)
+        ok = True
+        for mode in ("nccl", "p2p"):
+            sh = ShardedSampler(s.sample_rows, total, scatter=s.sample_rows_scatter if mode == "p2p" else None,
+                                device=dev)
+            lo, n = sh.start, sh.count
+            t = torch.from_numpy(x[lo:lo + n].view(np.int16)).to(dev).view(torch.bfloat16)
+            for _ in range(3):  # repeated steps reuse the exchange buffer
+                ids = sh.sample_rows(t, seeds_to_states(seeds[lo:lo + n], dev))
+                torch.cuda.synchronize()
+                ok = ok and np.array_equal(ids.cpu().numpy(), want)
+            dist.barrier()
+        s.close()
+        q.put((rank, ok))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_sharded_sampling_matches_single_gpu_tokens():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29600 + os.getpid() % 300
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in results), results
