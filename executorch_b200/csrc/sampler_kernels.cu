@@ -102,9 +102,8 @@ struct __align__(16) Shared {
       int rank[kRankSortMax];
     } rsort;
     struct {
-      unsigned digit[kRadix];
-      unsigned offs[kRadix];
-      unsigned short wdig[kWarps][kRadix];
+      unsigned wofs[kWarps][kRadix];  // per warp and digit: count, then running output offset
+      unsigned above[kRadix];
     } radix;
   } u;
 };
@@ -582,67 +581,84 @@ __device__ __forceinline__ float row_max_scaled(
 // ---------------------------------------------------------------------------------------
 // Stable LSD radix sort pass over a list of n entries, descending in the 8-bit digit at
 // `shift`. One block; src and dst are distinct global buffers.
+//
+// Every warp owns a contiguous slice of the list. (1) Each warp counts the digits of its
+// slice into its own 256 counters. (2) One block-wide prefix turns the counters into start
+// offsets: digits in descending order, and within a digit the warps in order, which is the
+// list order. (3) Each warp scatters its slice in steps of 32 entries, ranking the lanes of
+// a step with a warp match and advancing its private offsets; no block barrier is needed
+// inside the scatter.
 // ---------------------------------------------------------------------------------------
 template <typename S>
 __device__ void radix_pass_desc(S& sm, const Entry* src, Entry* dst, int n, int shift) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  __syncthreads();
-  for (int d = tid; d < kRadix; d += kThreads) sm.u.radix.digit[d] = 0;
-  __syncthreads();
-  for (int i = tid; i < n; i += kThreads) {
-    atomicAdd(&sm.u.radix.digit[(src[i].key >> shift) & (kRadix - 1)], 1u);
+  unsigned (*wofs)[kRadix] = sm.u.radix.wofs;
+  const int per_warp = ((n + kWarps - 1) / kWarps + 31) & ~31;  // slice length, a multiple of 32
+  const int lo = warp * per_warp < n ? warp * per_warp : n;
+  const int hi = lo + per_warp < n ? lo + per_warp : n;
+  __syncthreads();  // earlier users of the union are done
+  for (int d = lane; d < kRadix; d += 32) wofs[warp][d] = 0;
+  __syncwarp();
+  for (int i0 = lo; i0 < hi; i0 += 32 * kListBatch) {
+    uint32_t k[kListBatch];
+#pragma unroll
+    for (int u = 0; u < kListBatch; ++u) {  // independent loads first, so they overlap
+      const int i = i0 + u * 32 + lane;
+      k[u] = i < hi ? src[i].key : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < kListBatch; ++u) {
+      if (i0 + u * 32 + lane < hi) atomicAdd(&wofs[warp][(k[u] >> shift) & (kRadix - 1)], 1u);
+    }
   }
   __syncthreads();
-  // offs[d] = number of entries with a larger digit (descending order): suffix sums over
-  // the 256 digits, 8 warps of 32 digits each
+  // thread d (< 256) walks digit d over the warps; the digit totals are then prefixed in
+  // descending digit order
+  unsigned digit_total = 0;
   if (tid < kRadix) {
-    const unsigned c = sm.u.radix.digit[tid];
-    unsigned incl = c;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const unsigned c = wofs[w][tid];
+      wofs[w][tid] = digit_total;  // entries of this digit in earlier warps
+      digit_total += c;
+    }
+    // suffix sums over the 256 digits: 8 warps of 32 digits each
+    unsigned incl = digit_total;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const unsigned o = __shfl_down_sync(0xffffffffu, incl, d);
       if (lane + d < 32) incl += o;
     }
-    sm.u.radix.offs[tid] = incl - c;
+    sm.u.radix.above[tid] = incl - digit_total;  // larger digits inside this group of 32
     if (lane == 0) sm.redi[warp] = (int)incl;
   }
   __syncthreads();
   if (tid < kRadix) {
-    unsigned above = 0;
+    unsigned above = sm.u.radix.above[tid];
     for (int w = warp + 1; w < kRadix / 32; ++w) above += (unsigned)sm.redi[w];
-    sm.u.radix.offs[tid] += above;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) wofs[w][tid] += above;
   }
   __syncthreads();
-  for (int base = 0; base < n; base += kThreads) {
-    const int i = base + tid;
-    const bool valid = i < n;
+  for (int i0 = lo; i0 < hi; i0 += 32) {
+    const int i = i0 + lane;
+    const bool valid = i < hi;
     Entry e;
     e.key = 0;
     e.idx = 0;
     if (valid) e = src[i];
     const unsigned dg = valid ? ((e.key >> shift) & (kRadix - 1)) : 0xFFFFFFFFu;
-    for (int d = lane; d < kRadix; d += 32) sm.u.radix.wdig[warp][d] = 0;
-    __syncwarp();
-    // rank among the lanes of this warp that hold the same digit, in lane (= list) order
+    // rank among the lanes of this step that hold the same digit, in lane (= list) order
     const unsigned peers = __match_any_sync(0xffffffffu, dg);
     const int rank = __popc(peers & ((1u << lane) - 1u));
-    if (valid && rank == 0) sm.u.radix.wdig[warp][dg] = (unsigned short)__popc(peers);
-    __syncthreads();
-    if (tid < kRadix) {
-      // per digit: turn the warps' counts into exclusive offsets; digit[] gets the tile total
-      unsigned run = 0;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        const unsigned c = sm.u.radix.wdig[w][tid];
-        sm.u.radix.wdig[w][tid] = (unsigned short)run;
-        run += c;
-      }
-      sm.u.radix.digit[tid] = run;
+    unsigned base = 0;
+    if (valid) base = wofs[warp][dg];
+    __syncwarp();
+    if (valid) {
+      dst[base + rank] = e;
+      if (rank == 0) wofs[warp][dg] = base + __popc(peers);
     }
-    __syncthreads();
-    if (valid) dst[sm.u.radix.offs[dg] + sm.u.radix.wdig[warp][dg] + rank] = e;
-    __syncthreads();
-    if (tid < kRadix) sm.u.radix.offs[tid] += sm.u.radix.digit[tid];
+    __syncwarp();
   }
   __syncthreads();
 }
@@ -952,7 +968,10 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     int* __restrict__ status) {
   (void)status;
   using S = Shared<kLut>;
-  __shared__ S sm;
+  // the block's shared state exceeds the 48 KB static limit: dynamic shared memory, sized
+  // sizeof(S) by the launcher
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  S& sm = *reinterpret_cast<S*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
   if (tid < 3) sm.two_parity[tid] = 0;
@@ -1365,12 +1384,22 @@ size_t sampler_scratch_bytes(int vocab, int blocks) {
 
 int sampler_threads() { return kThreads; }
 
+// Opts the kernel in to its dynamic shared-memory size (once per device would do; the call is
+// cheap and idempotent).
+template <typename T, bool kLut>
+static cudaError_t prepare_sample_kernel() {
+  return cudaFuncSetAttribute(sample_rows_kernel<T, kLut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)sizeof(Shared<kLut>));
+}
+
 template <typename T, bool kLut>
 static cudaError_t launch_sample_t(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
     int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, void* scratch,
     int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
-  sample_rows_kernel<T, kLut><<<blocks, kThreads, 0, stream>>>(
+  const cudaError_t attr = prepare_sample_kernel<T, kLut>();
+  if (attr != cudaSuccess) return attr;
+  sample_rows_kernel<T, kLut><<<blocks, kThreads, sizeof(Shared<kLut>), stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       peers,
       static_cast<Entry*>(scratch), table, status);
@@ -1429,13 +1458,22 @@ int sample_kernel_max_blocks_per_sm(int dtype) {
   cudaError_t e;
   switch (dtype) {
     case kDtypeFloat:
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float, false>, kThreads, 0);
+      e = prepare_sample_kernel<float, false>();
+      if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float, false>, kThreads,
+                                                          sizeof(Shared<false>));
       break;
     case kDtypeHalf:
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half, false>, kThreads, 0);
+      e = prepare_sample_kernel<__half, false>();
+      if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half, false>, kThreads,
+                                                          sizeof(Shared<false>));
       break;
     default:
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16, true>, kThreads, 0);
+      e = prepare_sample_kernel<__nv_bfloat16, true>();
+      if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16, true>,
+                                                          kThreads, sizeof(Shared<true>));
       break;
   }
   if (e != cudaSuccess || n < 1) n = 1;
