@@ -22,6 +22,7 @@ struct etb200_sampler {
   int topk = 0;
   unsigned long long* d_state = nullptr;  // the handle's own xorshift64* state
   int64_t* d_token = nullptr;             // output slot of the single-row call
+  int64_t* h_token = nullptr;             // its pinned host mirror (fast read-back)
   int* d_status = nullptr;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
@@ -33,6 +34,7 @@ struct etb200_sampler {
   int64_t* d_stage_ids = nullptr;
   int64_t stage_rows = 0;
   uint64_t launches = 0;
+  int blocks_per_sm[3] = {0, 0, 0};  // occupancy of the sampling kernel per dtype, queried once
   ExpTable table;
 };
 
@@ -132,6 +134,7 @@ etb200_error_t create_impl(
   h->sm_count = prop.multiProcessorCount;
   e = cudaMalloc(&h->d_state, sizeof(unsigned long long));
   if (e == cudaSuccess) e = cudaMalloc(&h->d_token, sizeof(int64_t));
+  if (e == cudaSuccess) e = cudaMallocHost(&h->h_token, sizeof(int64_t));
   if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(int));
   unsigned long long s = seed;
@@ -140,6 +143,7 @@ etb200_error_t create_impl(
     cudaFree(h->d_state);
     cudaFree(h->d_token);
     cudaFree(h->d_status);
+    cudaFreeHost(h->h_token);
     delete h;
     return fail(ETB200_MEMORY_ALLOCATION_FAILED, "device allocation failed: %s", cudaGetErrorString(e));
   }
@@ -147,8 +151,10 @@ etb200_error_t create_impl(
   return ETB200_OK;
 }
 
-int grid_blocks(const etb200_sampler* h, int dtype, int64_t rows) {
-  const int64_t resident = (int64_t)h->sm_count * sample_kernel_max_blocks_per_sm(dtype);
+int grid_blocks(etb200_sampler* h, int dtype, int64_t rows) {
+  const int slot = dtype == kDtypeFloat ? 0 : (dtype == kDtypeHalf ? 1 : 2);
+  if (h->blocks_per_sm[slot] == 0) h->blocks_per_sm[slot] = sample_kernel_max_blocks_per_sm(dtype);
+  const int64_t resident = (int64_t)h->sm_count * h->blocks_per_sm[slot];
   return (int)(rows < resident ? rows : resident);
 }
 
@@ -243,6 +249,7 @@ etb200_error_t etb200_sampler_destroy(etb200_sampler_t* h) {
   cudaDeviceSynchronize();
   cudaFree(h->d_state);
   cudaFree(h->d_token);
+  cudaFreeHost(h->h_token);
   cudaFree(h->d_status);
   cudaFree(h->scratch);
   cudaFree(h->d_stage);
@@ -291,10 +298,9 @@ etb200_error_t etb200_sampler_sample(
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   err = sample_rows_device(h, logits_device, dtype, 1, h->vocab, nullptr, h->d_token, st);
   if (err != ETB200_OK) return err;
-  int64_t tok = 0;
-  ETB_CUDA(cudaMemcpyAsync(&tok, h->d_token, sizeof(tok), cudaMemcpyDeviceToHost, st));
+  ETB_CUDA(cudaMemcpyAsync(h->h_token, h->d_token, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
   ETB_CUDA(cudaStreamSynchronize(st));
-  *out_token = (int32_t)tok;
+  *out_token = (int32_t)*h->h_token;
   return ETB200_OK;
 }
 
