@@ -12,6 +12,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
+@pytest.fixture(scope="session", autouse=True)
+def built_library():
+    """The CUDA library is built in-tree; (re)build it when missing or stale and a compiler is
+    at hand, so that a fresh checkout can run the suite directly."""
+    import shutil
+    from executorch_b200 import build as b
+    if b.needs_build() and (shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc")):
+        b.build()
+    return b.LIB
+
+
 @pytest.fixture(scope="session")
 def restatement():
     import oracle
