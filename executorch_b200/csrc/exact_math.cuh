@@ -264,25 +264,32 @@ ETB_HD void seq_push_scaled(SeqSummary* s, float v, float inv_u) {
 // half-way between two integers (then the caller must redo the chunk with the two-parity
 // functions, because the result depends on the parity of N). A product that underflows to
 // zero without a real tie only costs that redo. v / u is clamped to 2^24; any chunk
-// containing such a term leaves the binade anyway. `inv_u24` is 2^-24 / u.
+// containing a term of 2^23 or more leaves the binade anyway, so its sum only has to stay
+// at or above 2^24, which float addition of non-negative terms guarantees; below 2^24 every
+// partial sum is an integer that a float holds exactly. `inv_u24` is 2^-24 / u.
 //
-// Written so that everything but the integer add is a float multiply or add: on the GPU the
-// integer/compare pipe is the scarce one.
-ETB_HD void seq_push_fast(int* acc, float* tie_prod, float v, float inv_u24) {
+// Seven float multiplies and adds and nothing else: on the GPU the integer/compare pipe is
+// the scarce one, so neither the sum nor the tie test touches it. (The scaling by 2^24
+// folds into the two fused multiply-adds, whose product is exact.)
+ETB_HD void seq_push_fast(float* acc, float* tie_prod, float v, float inv_u24) {
 #if defined(__CUDA_ARCH__)
-  const float t = __fmul_rn(__saturatef(__fmul_rn(v, inv_u24)), 16777216.0f);
-  const float tm = __fadd_rn(t, 8388608.0f);  // 2^23: the sum's low bits are the rounded t
-  const float d = __fsub_rn(t, __fsub_rn(tm, 8388608.0f));
+  const float c = __saturatef(__fmul_rn(v, inv_u24));
+  const float tm = __fmaf_rn(c, 16777216.0f, 8388608.0f);  // 2^23: rounds c * 2^24 to an integer
+  const float r = __fsub_rn(tm, 8388608.0f);
+  const float d = __fmaf_rn(c, 16777216.0f, -r);
+  *acc = __fadd_rn(*acc, r);
   *tie_prod = __fmul_rn(*tie_prod, __fsub_rn(fabsf(d), 0.5f));
 #else
   float c = v * inv_u24;
   c = c < 0.0f ? 0.0f : (c > 1.0f ? 1.0f : c);
+  if (!(c == c)) c = 0.0f;  // the device's saturating multiply turns NaN into 0
   const float t = c * 16777216.0f;
   const float tm = t + 8388608.0f;
-  const float d = t - (tm - 8388608.0f);
+  const float r = tm - 8388608.0f;
+  const float d = t - r;
+  *acc = *acc + r;
   *tie_prod = *tie_prod * (fabsf(d) - 0.5f);
 #endif
-  *acc += (int)(f32_bits(tm) - 0x4B000000u);
 }
 
 // 2^(126 - kb): 2^-24 / u as a float, representable for kb in [27, 252].

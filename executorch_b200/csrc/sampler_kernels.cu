@@ -188,11 +188,10 @@ __device__ __forceinline__ bool seqsum_tile(
         // v / u by an exact power-of-two scaling; adding 2^23 rounds it to an integer
         // (half to even) that can be read off the sum's bit pattern
         const float inv_u24 = seq_inv_u24(kb);
-        int acc = 0;
-        float tie_prod = 1.0f;
+        float accf = 0.0f, tie_prod = 1.0f;
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) seq_push_fast(&acc, &tie_prod, v[j], inv_u24);
-        acc = acc < kFastSat ? acc : kFastSat;
+        for (int j = 0; j < kChunk; ++j) seq_push_fast(&accf, &tie_prod, v[j], inv_u24);
+        const int acc = (int)fminf(accf, (float)kFastSat);
         mine.a0 = acc;
         mine.a1 = acc;
         if (!(tie_prod != 0.0f)) {  // zero (a tie, or an underflowed product) or NaN
@@ -470,9 +469,8 @@ struct RowMath {
   }
   __device__ __forceinline__ void eval_raw(const Raw& r, const S& sm, float (&e)[kChunk]) const {
     constexpr int kPerVec = 16 / sizeof(T);
-    uint32_t all_and = 0xFFFFFFFFu, all_or = 0u;  // over the biased patterns of the chunk
-    (void)all_and;
-    (void)all_or;
+    uint32_t bad = 0u;  // bits 14..12 of a biased half that differ from 100, over the chunk
+    (void)bad;
 #pragma unroll
     for (int q = 0; q < kRawVecs; ++q) {
       if constexpr (S::kHasLut) {
@@ -483,8 +481,7 @@ struct RowMath {
           // both halves at once. A carry out of the low half only happens for a low pattern
           // that is outside the table anyway, and then the whole chunk is redone below.
           const uint32_t wb = w[j] + (kLutBias | (kLutBias << 16));
-          all_and &= wb;
-          all_or |= wb;
+          bad |= wb ^ 0x40004000u;
           const uint32_t off0 = ((wb << 2) & 0x3FFCu) | ((wb >> 1) & 0x4000u);
           const uint32_t off1 = ((wb >> 14) & 0x3FFCu) | ((wb >> 17) & 0x4000u);
           e[q * 8 + 2 * j] = *reinterpret_cast<const float*>(lut_bytes + off0);
@@ -498,7 +495,7 @@ struct RowMath {
     }
     if constexpr (S::kHasLut) {
       // every pattern is inside the table iff bits 14..12 of every biased half are 100
-      if ((all_and & 0x40004000u) != 0x40004000u || (all_or & 0x30003000u) != 0u) {
+      if ((bad & 0x70007000u) != 0u) {
         // rare: a zero, tiny, huge or non-finite logit in this chunk; redo the chunk element by
         // element (table where possible, direct evaluation otherwise)
 #pragma unroll
@@ -562,7 +559,19 @@ __device__ __forceinline__ float row_max_scaled(
       using T2 = decltype(neg_inf2(T()));
       const int nvec = vec_ok ? vocab / 8 : 0;
       T2 acc = neg_inf2(T());
-      for (int q = tid; q < nvec; q += kThreads) {
+      // this pass is the row's HBM read: four 128-bit loads in flight per thread
+      int q = tid;
+      for (; q + 3 * kThreads < nvec; q += 4 * kThreads) {
+        uint4 raw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) raw[k] = __ldg(reinterpret_cast<const uint4*>(row) + q + k * kThreads);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const T2* p = reinterpret_cast<const T2*>(&raw[k]);
+          acc = __hmax2(acc, __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3])));
+        }
+      }
+      for (; q < nvec; q += kThreads) {
         const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row) + q);
         const T2* p = reinterpret_cast<const T2*>(&raw);
         acc = __hmax2(acc, __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3])));
@@ -1086,9 +1095,21 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       int cnt = 0, inc = 0;
       unsigned cmask = 0;  // bit j: e[j] is a candidate
       if (use_list) {
-        // entries beyond the row are 0 and the floor is > 0, so they never count
+        // entries beyond the row are 0 and the floor is > 0, so they never count.
+        // e >= floor is e > f for the float f just below the floor; with B = 1 / ulp(f) the
+        // fused e * B - f * B is >= 1 in the first case and <= 0 otherwise, so its saturation
+        // is the indicator, and the indicators weighted by 2^j add up to the mask exactly:
+        // float multiply-adds only, none of the scarce compare/logic instructions.
+        const uint32_t fbits = f32_bits(floor_now) - 1u;  // floor_now >= 2^-100
+        const float big = bits_f32((277u - (fbits >> 23)) << 23);
+        const float neg_c = -__fmul_rn(bits_f32(fbits), big);
+        float maskf = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) cmask |= (e[j] >= floor_now) ? (1u << j) : 0u;
+        for (int j = 0; j < kChunk; ++j) {
+          const float ind = __saturatef(__fmaf_rn(e[j], big, neg_c));
+          maskf = __fmaf_rn(ind, (float)(1u << j), maskf);
+        }
+        cmask = (unsigned)maskf;
         cnt = __popc(cmask);
         inc = cnt;
 #pragma unroll
@@ -1107,17 +1128,20 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         const int pre = __reduce_add_sync(0xffffffffu, lane < warp ? wc : 0);
         const int tot = __reduce_add_sync(0xffffffffu, wc);
         int off = n_a + pre + inc - cnt;
-        // Candidates are rare (well under 1 % of the logits): visit only the positions j at
-        // which some lane of the warp has one.
+        // Candidates are rare (well under 1 % of the logits): visit only the groups of four
+        // positions in which some lane of the warp has one.
         const unsigned any = __reduce_or_sync(0xffffffffu, cmask);
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) {
-          if (any & (1u << j)) {  // warp-uniform
-            if (cmask & (1u << j)) {
-              Entry en;
-              en.key = f32_bits(e[j]);
-              en.idx = i0 + j;
-              listA[off++] = en;
+        for (int g = 0; g < kChunk; g += 4) {
+          if (any & (0xFu << g)) {  // warp-uniform
+#pragma unroll
+            for (int j = g; j < g + 4; ++j) {
+              if (cmask & (1u << j)) {
+                Entry en;
+                en.key = f32_bits(e[j]);
+                en.idx = i0 + j;
+                listA[off++] = en;
+              }
             }
           }
         }

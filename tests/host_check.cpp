@@ -28,10 +28,9 @@ bool tile(const float* v, int threads, int chunk, float& s, bool search, float t
         if (kb >= 27 && kb <= 252 && !force_generic) {
           // as the kernel: tie-free fast path first, two-parity redo of the chunk on a tie
           const float inv_u24 = seq_inv_u24(kb);
-          int acc = 0;
-          float tie_prod = 1.0f;
-          for (int j = 0; j < chunk; ++j) seq_push_fast(&acc, &tie_prod, v[t * chunk + j], inv_u24);
-          if (acc > (1 << 25)) acc = 1 << 25;
+          float accf = 0.0f, tie_prod = 1.0f;
+          for (int j = 0; j < chunk; ++j) seq_push_fast(&accf, &tie_prod, v[t * chunk + j], inv_u24);
+          const int acc = (int)(accf < 33554432.0f ? accf : 33554432.0f);
           mine[t].a0 = mine[t].a1 = acc;
           if (!(tie_prod != 0.0f)) {
             const float inv_u = seq_inv_u(kb);
