@@ -33,6 +33,12 @@ struct etb200_sampler {
   unsigned long long* d_stage_states = nullptr;
   int64_t* d_stage_ids = nullptr;
   int64_t stage_rows = 0;
+  // the host-buffer entry point copies in slices on its own stream while earlier slices are
+  // being sampled on the caller's stream
+  static constexpr int kMaxSlices = 8;
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t slice_ready[kMaxSlices] = {};
+  cudaEvent_t entry_event = nullptr;
   uint64_t launches = 0;
   int blocks_per_sm[3] = {0, 0, 0};  // occupancy of the sampling kernel per dtype, queried once
   ExpTable table;
@@ -255,6 +261,10 @@ etb200_error_t etb200_sampler_destroy(etb200_sampler_t* h) {
   cudaFree(h->d_stage);
   cudaFree(h->d_stage_states);
   cudaFree(h->d_stage_ids);
+  if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
+  for (cudaEvent_t ev : h->slice_ready)
+    if (ev) cudaEventDestroy(ev);
+  if (h->entry_event) cudaEventDestroy(h->entry_event);
   delete h;
   return ETB200_OK;
 }
@@ -376,14 +386,55 @@ etb200_error_t etb200_sampler_sample_rows_host(
                   cudaGetErrorString(e));
     h->stage_rows = rows;
   }
-  ETB_CUDA(cudaMemcpyAsync(h->d_stage, logits_host, bytes, cudaMemcpyHostToDevice, st));
   if (!greedy) {
     ETB_CUDA(cudaMemcpyAsync(h->d_stage_states, rng_states_host, sizeof(uint64_t) * (size_t)rows,
                              cudaMemcpyHostToDevice, st));
   }
-  err = sample_rows_device(h, h->d_stage, dtype, rows, row_stride_elems, h->d_stage_states,
-                           h->d_stage_ids, st);
-  if (err != ETB200_OK) return err;
+  // Large batches go in slices of whole rows: slice k+1 crosses PCIe on the handle's copy
+  // stream while slice k is sampled on the caller's stream, so that only the last slice's
+  // kernel is not hidden behind the copy. Slices stay above 32 rows and 4 MB each.
+  int slices = 1;
+  if (row_stride_elems >= h->vocab) {
+    const int64_t by_rows = rows / 32;
+    const int64_t by_bytes = (int64_t)(bytes >> 22);
+    int64_t n = by_rows < by_bytes ? by_rows : by_bytes;
+    if (n > etb200_sampler::kMaxSlices) n = etb200_sampler::kMaxSlices;
+    if (n > 1) slices = (int)n;
+  }
+  if (slices == 1) {
+    ETB_CUDA(cudaMemcpyAsync(h->d_stage, logits_host, bytes, cudaMemcpyHostToDevice, st));
+    err = sample_rows_device(h, h->d_stage, dtype, rows, row_stride_elems, h->d_stage_states,
+                             h->d_stage_ids, st);
+    if (err != ETB200_OK) return err;
+  } else {
+    if (!h->copy_stream) {
+      ETB_CUDA(cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+      ETB_CUDA(cudaEventCreateWithFlags(&h->entry_event, cudaEventDisableTiming));
+      for (cudaEvent_t& ev : h->slice_ready) ETB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    }
+    // the copies must not overtake work already queued on the caller's stream
+    ETB_CUDA(cudaEventRecord(h->entry_event, st));
+    ETB_CUDA(cudaStreamWaitEvent(h->copy_stream, h->entry_event, 0));
+    const int64_t per = (rows + slices - 1) / slices;
+    const char* src = static_cast<const char*>(logits_host);
+    char* dst = static_cast<char*>(h->d_stage);
+    for (int k = 0; k < slices; ++k) {
+      const int64_t r0 = k * per;
+      const int64_t n = (r0 + per <= rows) ? per : rows - r0;
+      if (n <= 0) break;
+      const size_t off = (size_t)r0 * (size_t)row_stride_elems * esz;
+      const size_t len = ((size_t)(n - 1) * (size_t)row_stride_elems + (size_t)h->vocab) * esz;
+      ETB_CUDA(cudaMemcpyAsync(dst + off, src + off, len, cudaMemcpyHostToDevice, h->copy_stream));
+      ETB_CUDA(cudaEventRecord(h->slice_ready[k], h->copy_stream));
+      ETB_CUDA(cudaStreamWaitEvent(st, h->slice_ready[k], 0));
+      err = sample_rows_device(h, dst + off, dtype, n, row_stride_elems, h->d_stage_states + r0,
+                               h->d_stage_ids + r0, st);
+      if (err != ETB200_OK) {
+        cudaStreamSynchronize(h->copy_stream);
+        return err;
+      }
+    }
+  }
   ETB_CUDA(cudaMemcpyAsync(out_ids_host, h->d_stage_ids, sizeof(int64_t) * (size_t)rows,
                            cudaMemcpyDeviceToHost, st));
   if (!greedy) {

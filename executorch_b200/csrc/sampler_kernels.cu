@@ -1270,69 +1270,66 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
 // index order: the lowest index among equal maxima wins, -0 equals +0, a NaN never
 // replaces the running maximum, and a NaN in element 0 is never replaced.
 // ---------------------------------------------------------------------------------------
-// Each thread keeps four 128-bit loads in flight per iteration: with one block per row and
-// fewer than two blocks per SM at batch 256, the bytes in flight decide the bandwidth.
-constexpr int kArgVecs = 4;
+// Each thread keeps eight 128-bit loads in flight per iteration, each of them contiguous
+// across the warp: with one block per row and fewer than two blocks per SM at batch 256, the
+// bytes in flight decide the bandwidth.
+constexpr int kArgVecs = 8;
 
 template <typename T, bool kRawU16>
 __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
     int64_t* __restrict__ out_ids, PeerOut peers) {
   constexpr int kPerVec = 16 / sizeof(T);
-  constexpr int kArgChunk = kArgVecs * kPerVec;  // consecutive logits per thread per iteration
   __shared__ float sv[kWarps];
   __shared__ int si[kWarps];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const T* row = logits + r * row_stride;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+    const uint4* row4 = reinterpret_cast<const uint4*>(row);
+    const int nvec = vec_ok ? vocab / kPerVec : 0;
     float best = -INFINITY;
     int besti = 0x7fffffff;  // "nothing better than -inf seen": resolved to the first index below
-    for (int base = 0; base < vocab; base += kThreads * kArgChunk) {
-      const int i0 = base + tid * kArgChunk;
-      float x[kArgChunk];
-      if (vec_ok && i0 + kArgChunk <= vocab) {
-        uint4 raw[kArgVecs];
+    // A thread visits its elements in increasing index order (vector q * kThreads + tid of
+    // each group, then the ragged tail), so strict '>' keeps its lowest index of a maximum.
+    for (int v0 = 0; v0 < nvec; v0 += kThreads * kArgVecs) {
+      uint4 raw[kArgVecs];
 #pragma unroll
-        for (int q = 0; q < kArgVecs; ++q) raw[q] = __ldg(reinterpret_cast<const uint4*>(row + i0) + q);
+      for (int q = 0; q < kArgVecs; ++q) {
+        const int v = v0 + q * kThreads + tid;
+        if (v < nvec) raw[q] = __ldg(row4 + v);
+      }
 #pragma unroll
-        for (int q = 0; q < kArgVecs; ++q) {
+      for (int q = 0; q < kArgVecs; ++q) {
+        const int v = v0 + q * kThreads + tid;
+        if (v < nvec) {
           const T* p = reinterpret_cast<const T*>(&raw[q]);
 #pragma unroll
           for (int j = 0; j < kPerVec; ++j) {
+            float x;
             if constexpr (kRawU16) {
-              x[q * kPerVec + j] = (float)p[j];  // sample<uint16_t> compares the raw integers
+              x = (float)p[j];  // sample<uint16_t> compares the raw integers
             } else {
-              x[q * kPerVec + j] = to_f32(p[j]);
+              x = to_f32(p[j]);
+            }
+            if (x > best) {
+              best = x;
+              besti = v * kPerVec + j;
             }
           }
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < kArgChunk; ++j) {
-          if constexpr (kRawU16) {
-            x[j] = (i0 + j < vocab) ? (float)row[i0 + j] : 0.0f;
-          } else {
-            x[j] = (i0 + j < vocab) ? to_f32(row[i0 + j]) : 0.0f;
-          }
-        }
       }
-      if (i0 + kArgChunk <= vocab) {
-#pragma unroll
-        for (int j = 0; j < kArgChunk; ++j) {
-          if (x[j] > best) {
-            best = x[j];
-            besti = i0 + j;
-          }
-        }
+    }
+    for (int i = nvec * kPerVec + tid; i < vocab; i += kThreads) {
+      float x;
+      if constexpr (kRawU16) {
+        x = (float)row[i];
       } else {
-#pragma unroll
-        for (int j = 0; j < kArgChunk; ++j) {
-          if (i0 + j < vocab && x[j] > best) {
-            best = x[j];
-            besti = i0 + j;
-          }
-        }
+        x = to_f32(row[i]);
+      }
+      if (x > best) {
+        best = x;
+        besti = i;
       }
     }
     // combine: larger value wins, equal values keep the lower index

@@ -453,6 +453,27 @@ def test_host_buffer_entry_matches_device_entry(cuda_device, restatement):
     s.close()
 
 
+def test_host_buffer_entry_in_slices(cuda_device, restatement):
+    """A batch large enough (100 rows, 12.8 MB) for the host-buffer entry point to copy in
+    slices on its own stream while sampling earlier slices; ragged last slice; both the
+    sampling and the greedy kernel; called twice so that the second call reuses the streams
+    and events."""
+    rows, vocab = 100, 32000
+    x = W.rows_numpy("c1", list(range(rows)), vocab=vocab)
+    seeds = np.arange(rows, dtype=np.uint64) * np.uint64(7919) + np.uint64(3)
+    s = Sampler(vocab, 0.8, 0.9, 0, device=cuda_device)
+    want, wst = restatement.sample_rows(x, 0.8, 0.9, seeds, dtype="fp32", return_states=True)
+    for _ in range(2):
+        st = seeds.copy()
+        got = s.sample_rows_host(x, st, dtype="fp32")
+        assert np.array_equal(got, want)
+        assert np.array_equal(st, wst)
+    s.set_temperature(0.0)
+    assert np.array_equal(s.sample_rows_host(x, None, dtype="fp32"),
+                          restatement.sample_rows(x, 0.0, 0.9, seeds, dtype="fp32"))
+    s.close()
+
+
 def test_chi_square_one_million_draws(cuda_device, restatement):
     """10^6 draws from one fixed config-3 row against the oracle's own nucleus distribution,
     top-p and multinomial; coins from 10^6 different seeds (a stride-0 batch)."""
