@@ -188,9 +188,14 @@ __device__ __forceinline__ bool seqsum_tile(
         // v / u by an exact power-of-two scaling; adding 2^23 rounds it to an integer
         // (half to even) that can be read off the sum's bit pattern
         const float inv_u24 = seq_inv_u24(kb);
-        float accf = 0.0f, tie_prod = 1.0f;
+        // four interleaved accumulator pairs: short dependency chains (the partial sums are
+        // integers below 2^24, hence exact, whenever the total is; otherwise the total stays
+        // at or above 2^24, which is all that matters then)
+        float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, t4[4] = {1.0f, 1.0f, 1.0f, 1.0f};
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) seq_push_fast(&accf, &tie_prod, v[j], inv_u24);
+        for (int j = 0; j < kChunk; ++j) seq_push_fast(&a4[j & 3], &t4[j & 3], v[j], inv_u24);
+        const float accf = __fadd_rn(__fadd_rn(a4[0], a4[1]), __fadd_rn(a4[2], a4[3]));
+        const float tie_prod = __fmul_rn(__fmul_rn(t4[0], t4[1]), __fmul_rn(t4[2], t4[3]));
         const int acc = (int)fminf(accf, (float)kFastSat);
         mine.a0 = acc;
         mine.a1 = acc;
@@ -208,19 +213,39 @@ __device__ __forceinline__ bool seqsum_tile(
       if (mine.a1 > kFastSat) mine.a1 = kFastSat;
     }
     if (mine.a0 != mine.a1) sm.two_parity[rp] = 1;
+    {
+      const int wtot = __reduce_add_sync(0xffffffffu, mine.a0);  // <= 32 * kFastSat
+      if (lane == 0) sm.wsum_i[rp][warp] = wtot < kFastSat ? wtot : kFastSat;
+    }
+    __syncthreads();  // ---- barrier 1: warp totals (and the two-parity flag) are visible
+    const int next_rp = rp == 2 ? 0 : rp + 1;
+    if (tid == 0) sm.two_parity[next_rp == 2 ? 0 : next_rp + 1] = 0;  // slot of the round after next
+    const bool two_parity = sm.two_parity[rp] != 0;
+    if (!two_parity) {
+      // The common round: N only grows along the tile, so if the value behind the whole tile
+      // is still inside the binade (and not beyond thr), nothing in between left it: the
+      // tile total is all that is needed, one reduction and no prefix sums.
+      const int n_end = n_s + __reduce_add_sync(0xffffffffu, (lane < kWarps) ? sm.wsum_i[rp][lane] : 0);
+      bool more = n_end >= kSeqLimit;
+      if (kSearch) {
+        if (!more && seq_value(kb, n_end) > thr) more = true;
+      }
+      if (!more) {
+        s = seq_value(kb, n_end);
+        rp = next_rp;
+        return false;
+      }
+    }
+    // Some chunk leaves the binade (or holds the searched position, or has a tie): prefix sums
     int inc = mine.a0;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const int o = __shfl_up_sync(0xffffffffu, inc, d);
       if (lane >= d) inc += o;
     }
-    if (lane == 31) sm.wsum_i[rp][warp] = inc < kFastSat ? inc : kFastSat;
-    __syncthreads();  // ---- barrier 1: warp totals (and the two-parity flag) are visible
-    const int next_rp = rp == 2 ? 0 : rp + 1;
-    if (tid == 0) sm.two_parity[next_rp == 2 ? 0 : next_rp + 1] = 0;  // slot of the round after next
     int n_in, n_out;       // N in front of / behind this thread's chunk
     int n_wend;            // N behind the warp `lane` (lanes < kWarps), for the warp-level decision
-    if (!sm.two_parity[rp]) {
+    if (!two_parity) {
       int wt = (lane < kWarps) ? sm.wsum_i[rp][lane] : 0;
 #pragma unroll
       for (int d = 1; d < kWarps; d <<= 1) {
@@ -1103,13 +1128,13 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         const uint32_t fbits = f32_bits(floor_now) - 1u;  // floor_now >= 2^-100
         const float big = bits_f32((277u - (fbits >> 23)) << 23);
         const float neg_c = -__fmul_rn(bits_f32(fbits), big);
-        float maskf = 0.0f;
+        float m4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // interleaved: short dependency chains
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) {
           const float ind = __saturatef(__fmaf_rn(e[j], big, neg_c));
-          maskf = __fmaf_rn(ind, (float)(1u << j), maskf);
+          m4[j & 3] = __fmaf_rn(ind, (float)(1u << j), m4[j & 3]);
         }
-        cmask = (unsigned)maskf;
+        cmask = (unsigned)((m4[0] + m4[1]) + (m4[2] + m4[3]));
         cnt = __popc(cmask);
         inc = cnt;
 #pragma unroll

@@ -28,8 +28,10 @@ bool tile(const float* v, int threads, int chunk, float& s, bool search, float t
         if (kb >= 27 && kb <= 252 && !force_generic) {
           // as the kernel: tie-free fast path first, two-parity redo of the chunk on a tie
           const float inv_u24 = seq_inv_u24(kb);
-          float accf = 0.0f, tie_prod = 1.0f;
-          for (int j = 0; j < chunk; ++j) seq_push_fast(&accf, &tie_prod, v[t * chunk + j], inv_u24);
+          float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, t4[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+          for (int j = 0; j < chunk; ++j) seq_push_fast(&a4[j & 3], &t4[j & 3], v[t * chunk + j], inv_u24);
+          const float accf = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+          const float tie_prod = (t4[0] * t4[1]) * (t4[2] * t4[3]);
           const int acc = (int)(accf < 33554432.0f ? accf : 33554432.0f);
           mine[t].a0 = mine[t].a1 = acc;
           if (!(tie_prod != 0.0f)) {
