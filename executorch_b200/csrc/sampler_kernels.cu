@@ -63,6 +63,9 @@ constexpr int kRankSortMax = 512;           // survivor lists up to this size ar
 // (5 exponent bits, 7 mantissa bits) plus the sign as bit 12.
 constexpr uint32_t kLutBias = (128u - (127u - 16u)) << 7;  // 0x0880
 constexpr int kLutSize = 8192;
+// A thread's kChunk staged terms are followed by 4 floats of padding: 128-bit reads of
+// consecutive runs by consecutive lanes then fall into distinct banks.
+constexpr int kStagePitch = kChunk + 4;
 
 struct Entry {
   uint32_t key;  // float bits of e_i (list A) or p_i (sorted lists); positive floats order like integers
@@ -92,6 +95,8 @@ struct __align__(16) Shared {
   int misc_i[4];
   float misc_f[4];
   union {
+    // terms of the row's first tile, one padded run per thread, for the one-warp start of the sum
+    alignas(16) float stage[kThreads * kStagePitch];
     unsigned wbins[kWarps / 2][kBins][2];  // per warp pair and value bin: count, sum of mantissa offsets
     struct {
       unsigned short cnt[kCompactSteps][kWarps];  // survivors per (step, warp), then exclusive in step
@@ -149,6 +154,141 @@ __device__ __forceinline__ int block_excl_count(S& sm, int cnt, int* total) {
   return pre + inc - cnt;
 }
 
+// Summary of one thread's chunk in the binade kb of the running sum: the tie-free fast path
+// first, the two-parity functions when the chunk holds an exact half-way term (or for sums
+// outside the fast path's range).
+__device__ __forceinline__ SeqSummary chunk_summary(const float (&v)[kChunk], int kb) {
+  SeqSummary mine;
+  seq_identity(&mine);
+  if (kb >= 27 && kb <= 252) {
+    // v / u by an exact power-of-two scaling; adding 2^23 rounds it to an integer (half to
+    // even). Four interleaved accumulator pairs: short dependency chains (the partial sums
+    // are integers below 2^24, hence exact, whenever the total is; otherwise the total
+    // stays at or above 2^24, which is all that matters then).
+    const float inv_u24 = seq_inv_u24(kb);
+    float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, t4[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) seq_push_fast(&a4[j & 3], &t4[j & 3], v[j], inv_u24);
+    const float accf = __fadd_rn(__fadd_rn(a4[0], a4[1]), __fadd_rn(a4[2], a4[3]));
+    const float tie_prod = __fmul_rn(__fmul_rn(t4[0], t4[1]), __fmul_rn(t4[2], t4[3]));
+    const int acc = (int)fminf(accf, (float)kFastSat);
+    mine.a0 = acc;
+    mine.a1 = acc;
+    if (!(tie_prod != 0.0f)) {  // zero (a tie, or an underflowed product) or NaN
+      const float inv_u = seq_inv_u(kb);
+      seq_identity(&mine);
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) seq_push_scaled(&mine, v[j], inv_u);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) seq_push(&mine, v[j], kb);
+  }
+  if (mine.a0 > kFastSat) mine.a0 = kFastSat;
+  if (mine.a1 > kFastSat) mine.a1 = kFastSat;
+  return mine;
+}
+
+// ---------------------------------------------------------------------------------------
+// The same exact sequential sum at warp scope: lane l holds the kChunk terms that follow
+// those of lanes 0..l-1; `s` is warp-uniform. No shared memory and no block barrier, so a
+// round costs one warp's instructions instead of the whole block's. Used where the running
+// sum leaves its binade every few hundred terms (the start of a row). Same contract as
+// seqsum_tile otherwise (pos0 = position of lane 0's first term).
+// ---------------------------------------------------------------------------------------
+template <bool kSearch>
+__device__ __forceinline__ bool seqsum_warp(
+    const float (&v)[kChunk], float& s, float thr, int pos0, int limit, int* hit_pos,
+    float* hit_sum) {
+  const int lane = threadIdx.x & 31;
+  int consumed = 0;
+  while (true) {
+    const int kb = seq_kb(s);
+    const int n_s = seq_n(s);
+    SeqSummary mine;
+    seq_identity(&mine);
+    const bool active = lane >= consumed;
+    if (active) mine = chunk_summary(v, kb);
+    const bool two_parity = __any_sync(0xffffffffu, mine.a0 != mine.a1);
+    if (!two_parity) {
+      const int n_end = n_s + __reduce_add_sync(0xffffffffu, mine.a0);  // <= 2^24 + 32 * kFastSat
+      bool more = n_end >= kSeqLimit;
+      if (kSearch) {
+        if (!more && seq_value(kb, n_end) > thr) more = true;
+      }
+      if (!more) {
+        s = seq_value(kb, n_end);
+        return false;
+      }
+    }
+    int n_in, n_out;  // N in front of / behind this lane's chunk
+    if (!two_parity) {
+      int inc = mine.a0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      n_in = n_s + (inc - mine.a0);
+      n_out = n_s + inc;
+    } else {
+      SeqSummary sc = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        SeqSummary o;
+        o.a0 = __shfl_up_sync(0xffffffffu, sc.a0, d);
+        o.a1 = __shfl_up_sync(0xffffffffu, sc.a1, d);
+        if (lane >= d) sc = seq_compose(o, sc);
+      }
+      SeqSummary excl;
+      excl.a0 = __shfl_up_sync(0xffffffffu, sc.a0, 1);
+      excl.a1 = __shfl_up_sync(0xffffffffu, sc.a1, 1);
+      if (lane == 0) seq_identity(&excl);
+      n_in = seq_apply(n_s, excl);
+      n_out = seq_apply(n_in, mine);
+    }
+    // the first chunk whose end value left the binade or, when searching, exceeds thr
+    bool flag = active && n_out >= kSeqLimit;
+    if (kSearch) {
+      if (active && n_out < kSeqLimit && seq_value(kb, n_out) > thr) flag = true;
+    }
+    const unsigned lb = __ballot_sync(0xffffffffu, flag);
+    if (lb == 0) {
+      s = seq_value(kb, __shfl_sync(0xffffffffu, n_out, 31));
+      return false;
+    }
+    const int first = __ffs(lb) - 1;
+    float acc = 0.0f, hval = 0.0f;
+    int found = 0, hpos = 0;
+    if (lane == first) {
+      // the sum in front of this chunk is exact: redo the chunk with real float additions
+      acc = seq_value(kb, n_in);
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) {
+        acc = __fadd_rn(acc, v[j]);
+        if (kSearch) {
+          const int pos = pos0 + lane * kChunk + j;
+          if (!found && acc > thr && pos < limit) {
+            found = 1;
+            hpos = pos;
+            hval = acc;
+          }
+        }
+      }
+    }
+    s = __shfl_sync(0xffffffffu, acc, first);
+    if (kSearch) {
+      if (__shfl_sync(0xffffffffu, found, first)) {
+        *hit_pos = __shfl_sync(0xffffffffu, hpos, first);
+        *hit_sum = __shfl_sync(0xffffffffu, hval, first);
+        return true;
+      }
+    }
+    consumed = first + 1;
+    if (consumed >= 32) return false;
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // One tile of the exact sequential float sum. Thread t holds the kChunk consecutive terms
 // v[] that follow the terms of threads 0..t-1. `s` is the running sum in front of the
@@ -183,35 +323,7 @@ __device__ __forceinline__ bool seqsum_tile(
     SeqSummary mine;
     seq_identity(&mine);
     const bool active = tid >= consumed;
-    if (active) {
-      if (kb >= 27 && kb <= 252) {
-        // v / u by an exact power-of-two scaling; adding 2^23 rounds it to an integer
-        // (half to even) that can be read off the sum's bit pattern
-        const float inv_u24 = seq_inv_u24(kb);
-        // four interleaved accumulator pairs: short dependency chains (the partial sums are
-        // integers below 2^24, hence exact, whenever the total is; otherwise the total stays
-        // at or above 2^24, which is all that matters then)
-        float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, t4[4] = {1.0f, 1.0f, 1.0f, 1.0f};
-#pragma unroll
-        for (int j = 0; j < kChunk; ++j) seq_push_fast(&a4[j & 3], &t4[j & 3], v[j], inv_u24);
-        const float accf = __fadd_rn(__fadd_rn(a4[0], a4[1]), __fadd_rn(a4[2], a4[3]));
-        const float tie_prod = __fmul_rn(__fmul_rn(t4[0], t4[1]), __fmul_rn(t4[2], t4[3]));
-        const int acc = (int)fminf(accf, (float)kFastSat);
-        mine.a0 = acc;
-        mine.a1 = acc;
-        if (!(tie_prod != 0.0f)) {  // zero (a tie, or an underflowed product) or NaN
-          const float inv_u = seq_inv_u(kb);
-          seq_identity(&mine);
-#pragma unroll
-          for (int j = 0; j < kChunk; ++j) seq_push_scaled(&mine, v[j], inv_u);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < kChunk; ++j) seq_push(&mine, v[j], kb);
-      }
-      if (mine.a0 > kFastSat) mine.a0 = kFastSat;
-      if (mine.a1 > kFastSat) mine.a1 = kFastSat;
-    }
+    if (active) mine = chunk_summary(v, kb);
     if (mine.a0 != mine.a1) sm.two_parity[rp] = 1;
     {
       const int wtot = __reduce_add_sync(0xffffffffu, mine.a0);  // <= 32 * kFastSat
@@ -1146,7 +1258,18 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       }
       int hp;
       float hs;
-      seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
+      const bool first_tile = base == kHead;  // block-uniform
+      if (first_tile) {
+        // The running sum leaves its binade every few hundred terms here, and every such
+        // round would occupy the whole block: stage the tile's terms in shared memory and
+        // let one warp sum them, 512 at a time, while the others list their candidates.
+        float4* st4 = reinterpret_cast<float4*>(sm.u.stage + tid * kStagePitch);
+#pragma unroll
+        for (int q = 0; q < kChunk / 4; ++q) st4[q] = make_float4(e[4 * q], e[4 * q + 1], e[4 * q + 2], e[4 * q + 3]);
+        __syncthreads();  // the staged terms and the candidate counts are visible
+      } else {
+        seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
+      }
       if (use_list) {
         // candidates of the warps in front of this one, and of the whole tile
         const int wc = lane < kWarps ? sm.wcnt[buf][lane] : 0;
@@ -1172,6 +1295,29 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         }
         n_a += tot;
         buf ^= 1;
+      }
+      if (first_tile) {
+        if (warp == 0) {
+          const int span = (vocab - kHead) < kTile ? (vocab - kHead) : kTile;
+          const int n_sub = (span + 32 * kChunk - 1) / (32 * kChunk);
+          float sw = s;
+          for (int t = 0; t < n_sub; ++t) {
+            float v[kChunk];
+            const float4* p4 = reinterpret_cast<const float4*>(sm.u.stage + (t * 32 + lane) * kStagePitch);
+#pragma unroll
+            for (int q = 0; q < kChunk / 4; ++q) {
+              const float4 x = p4[q];
+              v[4 * q] = x.x;
+              v[4 * q + 1] = x.y;
+              v[4 * q + 2] = x.z;
+              v[4 * q + 3] = x.w;
+            }
+            seqsum_warp<false>(v, sw, 0.0f, 0, 0, &hp, &hs);
+          }
+          if (lane == 0) sm.s_bcast = sw;
+        }
+        __syncthreads();  // the sum behind the first tile; the staging buffer is free again
+        s = sm.s_bcast;
       }
     }
     const float sum = s;
