@@ -465,6 +465,59 @@ __device__ __forceinline__ bool seqsum_tile(
   }
 }
 
+// The tile behind the sequential head is where the running sum still leaves its binade every
+// few hundred terms, and every such round of seqsum_tile occupies the whole block. Instead the
+// tile's terms are staged in shared memory (stage_first_tile, which ends with a barrier) and
+// one warp sums them 512 at a time (sum_staged_tile, block-uniform result behind a barrier)
+// while the other warps wait or, between the two calls, do other work.
+template <typename S>
+__device__ __forceinline__ void stage_first_tile(S& sm, const float (&e)[kChunk]) {
+  float4* st4 = reinterpret_cast<float4*>(sm.u.stage + threadIdx.x * kStagePitch);
+#pragma unroll
+  for (int q = 0; q < kChunk / 4; ++q) st4[q] = make_float4(e[4 * q], e[4 * q + 1], e[4 * q + 2], e[4 * q + 3]);
+  __syncthreads();
+}
+
+template <bool kSearch, typename S>
+__device__ __forceinline__ bool sum_staged_tile(
+    S& sm, float& s, float thr, int vocab, int* hit_pos, float* hit_sum) {
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    const int span = (vocab - kHead) < kTile ? (vocab - kHead) : kTile;
+    const int n_sub = (span + 32 * kChunk - 1) / (32 * kChunk);
+    float sw = s, hs = 0.0f;
+    int hp = 0;
+    bool hit = false;
+    for (int t = 0; t < n_sub && !hit; ++t) {
+      float v[kChunk];
+      const float4* p4 = reinterpret_cast<const float4*>(sm.u.stage + (t * 32 + lane) * kStagePitch);
+#pragma unroll
+      for (int q = 0; q < kChunk / 4; ++q) {
+        const float4 x = p4[q];
+        v[4 * q] = x.x;
+        v[4 * q + 1] = x.y;
+        v[4 * q + 2] = x.z;
+        v[4 * q + 3] = x.w;
+      }
+      hit = seqsum_warp<kSearch>(v, sw, thr, kHead + t * 32 * kChunk, vocab, &hp, &hs);
+    }
+    if (lane == 0) {
+      sm.s_bcast = sw;
+      sm.hit_found = hit ? 1 : 0;
+      sm.hit_idx = hp;
+      sm.hit_val = hs;
+    }
+  }
+  __syncthreads();  // the result; the staging buffer is free again
+  s = sm.s_bcast;
+  const bool hit = kSearch && sm.hit_found;
+  if (hit) {
+    *hit_pos = sm.hit_idx;
+    *hit_sum = sm.hit_val;
+  }
+  return hit;
+}
+
 // The first terms of a sum leave a binade every few additions, which would cost one block
 // round each; instead one thread adds the `count` terms staged in sm.head with real float
 // additions. Same contract as seqsum_tile. Callers fill sm.head before the call and need no
@@ -1263,10 +1316,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         // The running sum leaves its binade every few hundred terms here, and every such
         // round would occupy the whole block: stage the tile's terms in shared memory and
         // let one warp sum them, 512 at a time, while the others list their candidates.
-        float4* st4 = reinterpret_cast<float4*>(sm.u.stage + tid * kStagePitch);
-#pragma unroll
-        for (int q = 0; q < kChunk / 4; ++q) st4[q] = make_float4(e[4 * q], e[4 * q + 1], e[4 * q + 2], e[4 * q + 3]);
-        __syncthreads();  // the staged terms and the candidate counts are visible
+        stage_first_tile(sm, e);  // its barrier also publishes the candidate counts
       } else {
         seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
       }
@@ -1296,29 +1346,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         n_a += tot;
         buf ^= 1;
       }
-      if (first_tile) {
-        if (warp == 0) {
-          const int span = (vocab - kHead) < kTile ? (vocab - kHead) : kTile;
-          const int n_sub = (span + 32 * kChunk - 1) / (32 * kChunk);
-          float sw = s;
-          for (int t = 0; t < n_sub; ++t) {
-            float v[kChunk];
-            const float4* p4 = reinterpret_cast<const float4*>(sm.u.stage + (t * 32 + lane) * kStagePitch);
-#pragma unroll
-            for (int q = 0; q < kChunk / 4; ++q) {
-              const float4 x = p4[q];
-              v[4 * q] = x.x;
-              v[4 * q + 1] = x.y;
-              v[4 * q + 2] = x.z;
-              v[4 * q + 3] = x.w;
-            }
-            seqsum_warp<false>(v, sw, 0.0f, 0, 0, &hp, &hs);
-          }
-          if (lane == 0) sm.s_bcast = sw;
-        }
-        __syncthreads();  // the sum behind the first tile; the staging buffer is free again
-        s = sm.s_bcast;
-      }
+      if (first_tile) sum_staged_tile<false>(sm, s, 0.0f, vocab, &hp, &hs);
     }
     const float sum = s;
     __syncthreads();
@@ -1343,7 +1371,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       for (int base = kHead; base < vocab && !hit; base += kTile) {
         float p[kChunk];
         rm.chunk(base + tid * kChunk, sm, p);
-        hit = seqsum_tile<true>(sm, p, cdf, rp, coin, base, vocab, &hp, &hs);
+        if (base == kHead) {
+          stage_first_tile(sm, p);
+          hit = sum_staged_tile<true>(sm, cdf, coin, vocab, &hp, &hs);
+        } else {
+          hit = seqsum_tile<true>(sm, p, cdf, rp, coin, base, vocab, &hp, &hs);
+        }
       }
       if (hit) token = hp;
     } else {
