@@ -106,6 +106,16 @@ struct __align__(16) Shared {
       unsigned long long ck[kRankSortMax];
       int rank[kRankSortMax];
     } rsort;
+    struct {  // the whole tail of a row with a short nucleus, in shared memory (small_tail)
+      unsigned long long ck[kRankSortMax];
+      alignas(16) float p[kRankSortMax + 8];  // read four at a time, one group ahead
+      int idx[kRankSortMax];
+      alignas(16) float prefix[kRankSortMax + 4];
+      int cnt;
+      int first_above;
+      int last;
+      float cum;
+    } small;
     struct {
       unsigned wofs[kWarps][kRadix];  // per warp and digit: count, then running output offset
       unsigned above[kRadix];
@@ -1156,6 +1166,117 @@ __device__ void sort_candidates(S& sm, Entry* listB, int n_b, Entry* spare) {
 }
 
 // ---------------------------------------------------------------------------------------
+// The rest of sample_topp / sample_topk for a row whose survivors (list entries at or above
+// the value threshold key_lo that pass the cutoff crop) number at most kRankSortMax, entirely
+// in shared memory: unordered compaction (the sort key carries the index, so the list order
+// does not matter), rank sort by (probability descending, index ascending), then one thread
+// replays the reference's cumulative sum (sampler.cpp:146-156, or the top-k sum of
+// sampler.cpp:105-108) and keeps every partial sum; the second loop of the reference
+// (sampler.cpp:162-169) adds the same numbers in the same order, so its cdf values are those
+// partial sums and the draw is a parallel lookup. Returns false, with nothing decided, when
+// the survivors do not fit or do not suffice (the caller then takes the general path).
+// `all_listed`: the list holds every entry that passes the crop and the threshold keeps all.
+// ---------------------------------------------------------------------------------------
+template <typename S>
+__device__ bool small_tail(
+    S& sm, const Entry* listA, int n_a, uint32_t key_lo, float sum, float cutoff, float topp,
+    int topk, bool use_topk, bool all_listed, float coin, int* token) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  __syncthreads();  // earlier users of the union are done
+  if (tid == 0) {
+    sm.u.small.cnt = 0;
+    sm.u.small.first_above = 0x7fffffff;
+    sm.u.small.last = -1;
+  }
+  __syncthreads();
+  for (int i0 = 0; i0 < n_a; i0 += kThreads) {
+    const int i = i0 + tid;
+    bool keep = false;
+    unsigned long long ck = 0ull;
+    if (i < n_a) {
+      const Entry en = listA[i];
+      if (en.key >= key_lo) {
+        const float p = __fdiv_rn(bits_f32(en.key), sum);
+        keep = use_topk || p >= cutoff;
+        ck = ((unsigned long long)f32_bits(p) << 32) | (uint32_t)(0x7FFFFFFF - en.idx);
+      }
+    }
+    const unsigned bal = __ballot_sync(0xffffffffu, keep);
+    if (bal != 0u) {
+      int base = 0;
+      if (lane == 0) base = atomicAdd(&sm.u.small.cnt, __popc(bal));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      const int slot = base + __popc(bal & ((1u << lane) - 1u));
+      if (keep && slot < kRankSortMax) sm.u.small.ck[slot] = ck;
+    }
+  }
+  __syncthreads();
+  const int n_b = sm.u.small.cnt;
+  if (n_b <= 0 || n_b > kRankSortMax) return false;
+  if (use_topk && n_b < topk && !all_listed) return false;
+  if (tid < n_b) {
+    const unsigned long long mine = sm.u.small.ck[tid];
+    int rank = 0;
+#pragma unroll 8
+    for (int j = 0; j < n_b; ++j) rank += sm.u.small.ck[j] > mine ? 1 : 0;
+    sm.u.small.p[rank] = bits_f32((uint32_t)(mine >> 32));
+    sm.u.small.idx[rank] = (int)(0x7FFFFFFFu - (uint32_t)(mine & 0xFFFFFFFFull));
+  }
+  __syncthreads();
+  // the terms beyond the ones that count read as zero (adding zero changes no partial sum)
+  const int lim = use_topk ? (topk < n_b ? topk : n_b) : n_b;
+  if (tid < 8) sm.u.small.p[lim + tid] = 0.0f;
+  __syncthreads();
+  if (tid == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(sm.u.small.p);
+    float4* pre4 = reinterpret_cast<float4*>(sm.u.small.prefix);
+    float acc = 0.0f;
+    int last = -1;
+    float4 q = p4[0];
+    for (int i = 0; i < lim; i += 4) {
+      const float4 nq = p4[(i >> 2) + 1];  // next group, ahead of the additions
+      const float a1 = __fadd_rn(acc, q.x);
+      const float a2 = __fadd_rn(a1, q.y);
+      const float a3 = __fadd_rn(a2, q.z);
+      const float a4 = __fadd_rn(a3, q.w);
+      pre4[i >> 2] = make_float4(a1, a2, a3, a4);
+      if (!use_topk && a4 > topp) {  // the partial sums only grow: the first one above topp
+        int k = 3;
+        float hv = a4;
+        if (a3 > topp) { k = 2; hv = a3; }
+        if (a2 > topp) { k = 1; hv = a2; }
+        if (a1 > topp) { k = 0; hv = a1; }
+        last = i + k;
+        acc = hv;
+        break;
+      }
+      acc = a4;
+      q = nq;
+    }
+    // top-k keeps its k entries; top-p keeps everything when the sum never exceeds topp
+    // (the "in case of rounding errors" branch, sampler.cpp:152), which is only known to be
+    // everything when all candidates were listed
+    if (use_topk || (last < 0 && all_listed)) last = lim - 1;
+    sm.u.small.last = last;
+    sm.u.small.cum = acc;
+  }
+  __syncthreads();
+  const int last = sm.u.small.last;
+  if (last < 0) return false;
+  const float r = __fmul_rn(coin, sm.u.small.cum);  // sampler.cpp:162
+  {
+    const bool above = tid <= last && sm.u.small.prefix[tid] > r;
+    const unsigned bal = __ballot_sync(0xffffffffu, above);
+    if (bal != 0u && lane == 0) atomicMin(&sm.u.small.first_above, (tid & ~31) + __ffs(bal) - 1);
+  }
+  __syncthreads();
+  const int fa = sm.u.small.first_above;
+  *token = sm.u.small.idx[fa <= last ? fa : last];
+  __syncthreads();  // the union may be reused by the caller
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------
 // The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
 // otherwise. Follows Sampler::sample<float> (sampler.cpp:222-251).
 // ---------------------------------------------------------------------------------------
@@ -1393,7 +1514,8 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       bool take_all = false;
       int n_b = 0, last_idx = 0;
       float cum = 0.0f;
-      bool have = false;
+      bool have = false, token_ready = false;
+      token = 0;
       for (int round = 0; round < 4 && !have; ++round) {
         int bin_lo = 0, kept = n_a;
         bool enough = true;
@@ -1403,6 +1525,17 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
           n_a = gather_candidates(rm, sm, listA, exact_floor);
           complete = true;
           continue;
+        }
+        if (!take_all && kept <= kRankSortMax) {
+          // short nucleus (the usual case): finish in shared memory
+          const uint32_t klo = bin_lo > 0 ? (uint32_t)(bin_lo + kBinBase) << kBinShift : 0u;
+          int tk;
+          if (small_tail(sm, listA, n_a, klo, sum, cutoff, topp, topk, use_topk, bin_lo == 0 && complete,
+                         coin, &tk)) {
+            token_ready = true;
+            token = tk;
+            break;
+          }
         }
         // The radix sort ping-pongs into the free space behind list A. If the survivors may
         // not fit there, list A itself is the spare buffer, which is only allowed when list A
@@ -1453,7 +1586,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
           take_all = true;  // the value threshold was too optimistic: take all candidates
         }
       }
-      if (n_b <= 0 || !have) {
+      if (token_ready) {
+        // decided by small_tail
+      } else if (n_b <= 0 || !have) {
         token = 0;  // no candidate at all (NaN rows): undefined in the reference
       } else {
         const float rr = __fmul_rn(coin, cum);  // sampler.cpp:162
