@@ -79,10 +79,8 @@ struct __align__(16) Shared {
   uint64_t exp_tab[kExpTableSize];
   float lut[kLut ? kLutSize : 2];
   alignas(16) float head[kHead];  // read as float4
-  SeqSummary wsum[kWarps];
-  int wsum_i[3][kWarps];  // slots used by successive scan rounds in rotation (see seqsum_tile)
+  SeqSummary wsum[3][kWarps];  // slots used by successive scan rounds in rotation (see seqsum_tile)
   int first[2];
-  int two_parity[3];
   int wcnt[2][kWarps];
   float redf[kWarps];
   int redi[kWarps];
@@ -304,17 +302,19 @@ __device__ __forceinline__ bool seqsum_warp(
 // v[] that follow the terms of threads 0..t-1. `s` is the running sum in front of the
 // tile on entry and behind it on return (block-uniform).
 //
-// Each round summarises every thread's chunk in the binade of s. The common case has no
-// exact half-way tie anywhere in the tile: then a chunk's summary is one integer and the
-// block scan is a plain integer prefix sum. A tie anywhere switches the round to the
-// two-parity summaries of exact_math.cuh (one more barrier).
+// Each round summarises every thread's chunk in the binade of s, and every warp its 32
+// chunks: one integer (a warp reduction) when none of them holds an exact half-way term,
+// else the two-parity summary of exact_math.cuh composed along the lanes. After ONE barrier
+// every warp reads the kWarps summaries and decides, redundantly and identically, whether
+// the value behind the tile is still inside the binade (and not beyond thr); then the tile
+// total, a reduction or a composition of kWarps summaries, is all that is needed. Otherwise
+// prefix sums down to the thread name the first chunk that leaves the binade (or holds the
+// searched position); its thread redoes it with real float additions and publishes the new
+// sum behind a second barrier, and the threads behind it go into the next round.
 //
 // Rounds rotate through three sets of shared slots (`rp`, block-uniform, carried by the
 // caller across tiles), so a round needs no barrier to protect its slots from the previous
-// round. A round costs ONE barrier when no chunk leaves the binade: once the warp totals
-// are visible, every warp works out redundantly which warp (if any) holds the first chunk to
-// redo. Only then does that warp redo the chunk and publish the new sum behind a second
-// barrier. Invariant at round entry: two_parity[rp] == 0.
+// round.
 //
 // With kSearch, also looks for the first term after which the running sum exceeds `thr`
 // (terms at position >= limit, counted from pos0 of thread 0's first term, must be zero
@@ -334,20 +334,64 @@ __device__ __forceinline__ bool seqsum_tile(
     seq_identity(&mine);
     const bool active = tid >= consumed;
     if (active) mine = chunk_summary(v, kb);
-    if (mine.a0 != mine.a1) sm.two_parity[rp] = 1;
-    {
+    // Warp summary: one integer when none of the warp's chunks holds an exact half-way term
+    // (a reduction), else the two-parity summary composed along the lanes (rare).
+    SeqSummary lane_excl;  // two-parity summary of the lanes in front of this one (tie warps only)
+    seq_identity(&lane_excl);
+    SeqSummary wsum;
+    const bool warp_tie = __any_sync(0xffffffffu, mine.a0 != mine.a1);
+    if (!warp_tie) {
       const int wtot = __reduce_add_sync(0xffffffffu, mine.a0);  // <= 32 * kFastSat
-      if (lane == 0) sm.wsum_i[rp][warp] = wtot < kFastSat ? wtot : kFastSat;
+      wsum.a0 = wsum.a1 = wtot < kFastSat ? wtot : kFastSat;
+    } else {
+      SeqSummary sc = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        SeqSummary o;
+        o.a0 = __shfl_up_sync(0xffffffffu, sc.a0, d);
+        o.a1 = __shfl_up_sync(0xffffffffu, sc.a1, d);
+        if (lane >= d) sc = seq_compose(o, sc);
+      }
+      lane_excl.a0 = __shfl_up_sync(0xffffffffu, sc.a0, 1);
+      lane_excl.a1 = __shfl_up_sync(0xffffffffu, sc.a1, 1);
+      if (lane == 0) seq_identity(&lane_excl);
+      wsum.a0 = __shfl_sync(0xffffffffu, sc.a0, 31);
+      wsum.a1 = __shfl_sync(0xffffffffu, sc.a1, 31);
     }
-    __syncthreads();  // ---- barrier 1: warp totals (and the two-parity flag) are visible
+    if (lane == 0) sm.wsum[rp][warp] = wsum;
+    __syncthreads();  // ---- barrier 1: the warp summaries are visible
+    SeqSummary wt;
+    seq_identity(&wt);
+    if (lane < kWarps) wt = sm.wsum[rp][lane];
     const int next_rp = rp == 2 ? 0 : rp + 1;
-    if (tid == 0) sm.two_parity[next_rp == 2 ? 0 : next_rp + 1] = 0;  // slot of the round after next
-    const bool two_parity = sm.two_parity[rp] != 0;
+    const bool two_parity = __any_sync(0xffffffffu, wt.a0 != wt.a1);
+    int n_wend;  // N behind the warp `lane` (lanes < kWarps), for the warp-level decision
     if (!two_parity) {
       // The common round: N only grows along the tile, so if the value behind the whole tile
       // is still inside the binade (and not beyond thr), nothing in between left it: the
       // tile total is all that is needed, one reduction and no prefix sums.
-      const int n_end = n_s + __reduce_add_sync(0xffffffffu, (lane < kWarps) ? sm.wsum_i[rp][lane] : 0);
+      const int n_end = n_s + __reduce_add_sync(0xffffffffu, wt.a0);
+      bool more = n_end >= kSeqLimit;
+      if (kSearch) {
+        if (!more && seq_value(kb, n_end) > thr) more = true;
+      }
+      if (!more) {
+        s = seq_value(kb, n_end);
+        rp = next_rp;
+        return false;
+      }
+      n_wend = 0;
+    } else {
+      // a tie somewhere: compose the kWarps summaries; exact as long as N stays in the binade
+#pragma unroll
+      for (int d = 1; d < kWarps; d <<= 1) {
+        SeqSummary o;
+        o.a0 = __shfl_up_sync(0xffffffffu, wt.a0, d);
+        o.a1 = __shfl_up_sync(0xffffffffu, wt.a1, d);
+        if (lane >= d) wt = seq_compose(o, wt);
+      }
+      n_wend = seq_apply(n_s, wt);
+      const int n_end = __shfl_sync(0xffffffffu, n_wend, kWarps - 1);
       bool more = n_end >= kSeqLimit;
       if (kSearch) {
         if (!more && seq_value(kb, n_end) > thr) more = true;
@@ -358,59 +402,43 @@ __device__ __forceinline__ bool seqsum_tile(
         return false;
       }
     }
-    // Some chunk leaves the binade (or holds the searched position, or has a tie): prefix sums
-    int inc = mine.a0;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int o = __shfl_up_sync(0xffffffffu, inc, d);
-      if (lane >= d) inc += o;
-    }
-    int n_in, n_out;       // N in front of / behind this thread's chunk
-    int n_wend;            // N behind the warp `lane` (lanes < kWarps), for the warp-level decision
+    // Some chunk leaves the binade (or holds the searched position): prefix sums per thread
+    int n_in, n_out;  // N in front of / behind this thread's chunk
     if (!two_parity) {
-      int wt = (lane < kWarps) ? sm.wsum_i[rp][lane] : 0;
+      int inc = mine.a0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      int wi = wt.a0;
 #pragma unroll
       for (int d = 1; d < kWarps; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, wt, d);
-        if (lane >= d) wt += o;
+        const int o = __shfl_up_sync(0xffffffffu, wi, d);
+        if (lane >= d) wi += o;
       }
-      int pre = __shfl_sync(0xffffffffu, wt, warp > 0 ? warp - 1 : 0);
+      int pre = __shfl_sync(0xffffffffu, wi, warp > 0 ? warp - 1 : 0);
       if (warp == 0) pre = 0;
-      n_wend = n_s + wt;
+      n_wend = n_s + wi;
       n_in = n_s + pre + (inc - mine.a0);
       n_out = n_in + mine.a0;
     } else {
-      SeqSummary sc = mine;
+      // wt holds the inclusive composition over the warps; tie-free warps have not formed
+      // their lanes' prefix yet
+      if (!warp_tie) {
+        int inc = mine.a0;
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        SeqSummary o;
-        o.a0 = __shfl_up_sync(0xffffffffu, sc.a0, d);
-        o.a1 = __shfl_up_sync(0xffffffffu, sc.a1, d);
-        if (lane >= d) sc = seq_compose(o, sc);
-      }
-      SeqSummary excl;
-      excl.a0 = __shfl_up_sync(0xffffffffu, sc.a0, 1);
-      excl.a1 = __shfl_up_sync(0xffffffffu, sc.a1, 1);
-      if (lane == 0) seq_identity(&excl);
-      if (lane == 31) sm.wsum[warp] = sc;
-      __syncthreads();  // ---- extra barrier of a two-parity round
-      // every warp redundantly scans the kWarps warp totals with shuffles
-      SeqSummary wt;
-      seq_identity(&wt);
-      if (lane < kWarps) wt = sm.wsum[lane];
-#pragma unroll
-      for (int d = 1; d < kWarps; d <<= 1) {
-        SeqSummary o;
-        o.a0 = __shfl_up_sync(0xffffffffu, wt.a0, d);
-        o.a1 = __shfl_up_sync(0xffffffffu, wt.a1, d);
-        if (lane >= d) wt = seq_compose(o, wt);
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += o;
+        }
+        lane_excl.a0 = lane_excl.a1 = inc - mine.a0;
       }
       SeqSummary pre;
       pre.a0 = __shfl_sync(0xffffffffu, wt.a0, warp > 0 ? warp - 1 : 0);
       pre.a1 = __shfl_sync(0xffffffffu, wt.a1, warp > 0 ? warp - 1 : 0);
       if (warp == 0) seq_identity(&pre);
-      n_wend = seq_apply(n_s, wt);
-      pre = seq_compose(pre, excl);
+      pre = seq_compose(pre, lane_excl);
       n_in = seq_apply(n_s, pre);
       n_out = seq_apply(n_in, mine);
     }
@@ -1294,7 +1322,6 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   S& sm = *reinterpret_cast<S*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
-  if (tid < 3) sm.two_parity[tid] = 0;
   int rp = 0;  // which set of scan-round slots the next round uses (see seqsum_tile)
   // Guessed floor under the values that matter (nucleus members / the k largest). Pass 2 lists
   // only e >= guess; if that turns out to be too high for a row, the row is regathered with
