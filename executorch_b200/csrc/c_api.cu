@@ -21,8 +21,8 @@ struct etb200_sampler {
   float topp = 0.9f;
   int topk = 0;
   unsigned long long* d_state = nullptr;  // the handle's own xorshift64* state
-  int64_t* d_token = nullptr;             // output slot of the single-row call
-  int64_t* h_token = nullptr;             // its pinned host mirror (fast read-back)
+  int64_t* h_token = nullptr;             // pinned, device-mapped host slot: the single-row call's
+  int64_t* h_token_dev = nullptr;         // kernel stores the token straight into it (no copy)
   int* d_status = nullptr;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
@@ -139,15 +139,14 @@ etb200_error_t create_impl(
   }
   h->sm_count = prop.multiProcessorCount;
   e = cudaMalloc(&h->d_state, sizeof(unsigned long long));
-  if (e == cudaSuccess) e = cudaMalloc(&h->d_token, sizeof(int64_t));
-  if (e == cudaSuccess) e = cudaMallocHost(&h->h_token, sizeof(int64_t));
+  if (e == cudaSuccess) e = cudaHostAlloc(&h->h_token, sizeof(int64_t), cudaHostAllocMapped);
+  if (e == cudaSuccess) e = cudaHostGetDevicePointer(&h->h_token_dev, h->h_token, 0);
   if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(int));
   unsigned long long s = seed;
   if (e == cudaSuccess) e = cudaMemcpy(h->d_state, &s, sizeof(s), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
     cudaFree(h->d_state);
-    cudaFree(h->d_token);
     cudaFree(h->d_status);
     cudaFreeHost(h->h_token);
     delete h;
@@ -254,7 +253,6 @@ etb200_error_t etb200_sampler_destroy(etb200_sampler_t* h) {
   DeviceGuard guard(h->device);
   cudaDeviceSynchronize();
   cudaFree(h->d_state);
-  cudaFree(h->d_token);
   cudaFreeHost(h->h_token);
   cudaFree(h->d_status);
   cudaFree(h->scratch);
@@ -306,9 +304,9 @@ etb200_error_t etb200_sampler_sample(
   if (err != ETB200_OK) return err;
   DeviceGuard guard(h->device);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  err = sample_rows_device(h, logits_device, dtype, 1, h->vocab, nullptr, h->d_token, st);
+  // the kernel's last store goes to mapped host memory: the read-back needs no copy of its own
+  err = sample_rows_device(h, logits_device, dtype, 1, h->vocab, nullptr, h->h_token_dev, st);
   if (err != ETB200_OK) return err;
-  ETB_CUDA(cudaMemcpyAsync(h->h_token, h->d_token, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
   ETB_CUDA(cudaStreamSynchronize(st));
   *out_token = (int32_t)*h->h_token;
   return ETB200_OK;
