@@ -260,6 +260,30 @@ def test_degenerate_distributions(cuda_device, restatement):
         assert np.array_equal(gpu_sample(xb, "bf16", 1.0, 0.9, seeds, cuda_device), want), name
 
 
+def test_nucleus_sizes_around_the_shared_memory_limit(cuda_device, restatement):
+    """Rows whose nucleus is a plateau of n equal logits (every comparison a tie, so the
+    index order decides) over a low background, for n on both sides of the 512 survivors that
+    the shared-memory tail takes; top-p that cuts inside the plateau, top-p that needs all of
+    it, and top-k below, at and above n."""
+    rng = np.random.default_rng(23)
+    vocab = 40_000
+    sizes = (1, 2, 31, 500, 511, 512, 513, 520, 700, 1500)
+    x = np.full((len(sizes), vocab), -14.0, dtype=np.float32)
+    x += (0.01 * rng.standard_normal(x.shape)).astype(np.float32)
+    for r, n in enumerate(sizes):
+        where = rng.permutation(vocab)[:n]
+        x[r, where] = 3.0
+        x[r, where[: max(1, n // 7)]] = 3.25  # a second, higher plateau inside it
+    seeds = rng.integers(0, 2**62, size=len(sizes)).astype(np.uint64)
+    for dtype in ("fp32", "bf16"):
+        xd = x if dtype == "fp32" else W.f32_to_bf16_bits(x)
+        for t, p, k in ((1.0, 0.6, 0), (1.0, 0.97, 0), (1.0, 0.9999, 0), (0.7, 0.9, 0),
+                        (1.0, 0.9, 400), (1.0, 0.9, 512), (1.0, 0.9, 515), (1.0, 0.9, 5000)):
+            want = restatement.sample_rows(xd, t, p, seeds, dtype=dtype, topk=k, threads=8)
+            got = gpu_sample(xd, dtype, t, p, seeds, cuda_device, topk=k)
+            assert np.array_equal(got, want), (dtype, t, p, k, np.nonzero(got != want)[0][:8])
+
+
 def test_mixed_batch_larger_than_the_grid(cuda_device, restatement):
     """More rows than resident blocks, so every block samples several rows in turn and carries
     its candidate-floor guess from one row to the next; peaked, Zipf-shaped, flat and one-hot
