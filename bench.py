@@ -176,8 +176,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
-                    help="N > 1: ids stored into the peers' buffers by the kernel (p2p) or all-gathered (nccl)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-in-kernel", "nccl"],
+                    help="N > 1: ids stored into the peers' buffers by the kernel, ranks synchronised by a barrier "
+                         "behind the launch (p2p) or by arrival marks inside it (p2p-in-kernel); or all-gathered (nccl)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -219,11 +220,13 @@ def main():
     exchange, exchange_name = None, "none"
     if world > 1:
         exchange_name = "all_gather of int64 ids (NCCL)"
-        if args.exchange == "p2p":
+        if args.exchange in ("p2p", "p2p-in-kernel"):
             try:
                 from executorch_b200.sharded import PeerIdExchange
                 exchange = PeerIdExchange(total_rows, dev)
-                exchange_name = "ids stored into every peer's buffer by the kernel epilogue + symmetric-memory barrier"
+                exchange_name = ("ids stored into every peer's buffer by the kernel epilogue + "
+                                 + ("arrival marks and a bounded wait at the end of the same launch"
+                                    if args.exchange == "p2p-in-kernel" else "symmetric-memory barrier"))
             except Exception as exc:  # symmetric memory unavailable: use the collective
                 exchange_name += f" (peer buffers unavailable: {type(exc).__name__})"
         # every rank must take the same path
@@ -232,8 +235,13 @@ def main():
         if int(flag) == 0:
             exchange = None
 
+    in_kernel_sync = args.exchange == "p2p-in-kernel"
+
     def step(i):
-        if exchange is not None:
+        if exchange is not None and in_kernel_sync:
+            sampler.sample_rows_exchange(bufs[i % NBUF], states, exchange.dest_ptrs, exchange.mark_ptrs, rank,
+                                         rank * rows, exchange.next_epoch())
+        elif exchange is not None:
             sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
             exchange.finish()
         else:
@@ -261,7 +269,11 @@ def main():
     t0.record()
     for i in range(args.steps):
         k_start[i].record()
-        if exchange is not None:
+        if exchange is not None and in_kernel_sync:
+            sampler.sample_rows_exchange(bufs[i % NBUF], states, exchange.dest_ptrs, exchange.mark_ptrs, rank,
+                                         rank * rows, exchange.next_epoch())
+            k_end[i].record()
+        elif exchange is not None:
             sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
             k_end[i].record()
             exchange.finish()
@@ -276,6 +288,8 @@ def main():
         dist.barrier()
     clock_info = clocks.stop() if rank == 0 else None
     launches = sampler.launch_count - launches0
+    if exchange is not None and in_kernel_sync and sampler.status != 0:
+        raise RuntimeError("an arrival wait of the in-kernel id exchange ran out: the ranks were not in step")
     elapsed_ms = t0.elapsed_time(t1)
     kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(k_start, k_end))
     if world > 1:

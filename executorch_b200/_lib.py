@@ -38,6 +38,11 @@ SYMBOLS = {
     "etb200_sampler_sample_rows_scatter": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
                                                         C.c_int64, C.c_void_p, C.POINTER(C.c_void_p),
                                                         C.c_int32, C.c_int64, C.c_void_p]),
+    "etb200_sampler_sample_rows_exchange": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
+                                                         C.c_int64, C.c_void_p, C.POINTER(C.c_void_p),
+                                                         C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                                         C.c_int64, C.c_uint64, C.c_void_p]),
+    "etb200_sampler_get_status": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_int32)]),
     "etb200_sampler_sample_rows_host": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
                                                      C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "etb200_sample_rows_static": (C.c_uint32, [C.c_int32, C.c_float, C.c_float, C.c_void_p, C.c_int32,

@@ -23,7 +23,8 @@ struct etb200_sampler {
   unsigned long long* d_state = nullptr;  // the handle's own xorshift64* state
   int64_t* h_token = nullptr;             // pinned, device-mapped host slot: the single-row call's
   int64_t* h_token_dev = nullptr;         // kernel stores the token straight into it (no copy)
-  int* d_status = nullptr;
+  int* d_status = nullptr;       // [0]: set by a kernel whose bounded wait ran out
+  int* d_blocks_done = nullptr;  // block counter of the arrival barrier, zero between launches
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   int sm_count = 0;
@@ -141,8 +142,9 @@ etb200_error_t create_impl(
   e = cudaMalloc(&h->d_state, sizeof(unsigned long long));
   if (e == cudaSuccess) e = cudaHostAlloc(&h->h_token, sizeof(int64_t), cudaHostAllocMapped);
   if (e == cudaSuccess) e = cudaHostGetDevicePointer(&h->h_token_dev, h->h_token, 0);
-  if (e == cudaSuccess) e = cudaMalloc(&h->d_status, sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&h->d_status, 2 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 2 * sizeof(int));
+  if (e == cudaSuccess) h->d_blocks_done = h->d_status + 1;
   unsigned long long s = seed;
   if (e == cudaSuccess) e = cudaMemcpy(h->d_state, &s, sizeof(s), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
@@ -185,11 +187,14 @@ etb200_error_t sample_rows_device(
     etb200_sampler* h, const void* logits, int dtype, int64_t rows, int64_t row_stride,
     unsigned long long* rng_states, int64_t* out_ids, cudaStream_t stream,
     const PeerOut& peers = PeerOut{}) {
-  if (rows == 0) return ETB200_OK;
-  if (h->inv_temperature == 0.0f) {
+  // a rank without rows still takes part in the arrival barrier: one block that only arrives
+  if (rows == 0 && peers.epoch == 0ull) return ETB200_OK;
+  if (h->inv_temperature == 0.0f || rows == 0) {
     // greedy: no coin is drawn and the RNG state does not move (sampler.cpp:226-228)
-    const int blocks = (int)(rows < (int64_t)h->sm_count * 4 ? rows : (int64_t)h->sm_count * 4);
-    ETB_CUDA(launch_argmax_rows(dtype, logits, rows, h->vocab, row_stride, out_ids, peers, blocks, stream));
+    int blocks = (int)(rows < (int64_t)h->sm_count * 4 ? rows : (int64_t)h->sm_count * 4);
+    if (blocks < 1) blocks = 1;
+    ETB_CUDA(launch_argmax_rows(rows == 0 ? kDtypeFloat : dtype, logits, rows, h->vocab, row_stride, out_ids, peers,
+                                blocks, h->d_status, stream));
     h->launches += 1;
     return ETB200_OK;
   }
@@ -345,6 +350,54 @@ etb200_error_t etb200_sampler_sample_rows_scatter(
       h, logits_device, dtype, rows, row_stride_elems,
       reinterpret_cast<unsigned long long*>(rng_states_device), nullptr,
       static_cast<cudaStream_t>(stream), peers);
+}
+
+etb200_error_t etb200_sampler_sample_rows_exchange(
+    etb200_sampler_t* h, const void* logits_device, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,
+    uint64_t* const* arrive_marks, int32_t n_dest, int32_t my_rank, int64_t dest_offset,
+    uint64_t epoch, void* stream) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  ETB_CHECK_ARG(dest_buffers != nullptr && arrive_marks != nullptr, "dest_buffers or arrive_marks is null");
+  ETB_CHECK_ARG(n_dest >= 1 && n_dest <= kMaxPeers, "n_dest must be in [1, %d], got %d", kMaxPeers, n_dest);
+  ETB_CHECK_ARG(my_rank >= 0 && my_rank < n_dest, "my_rank %d is outside [0, %d)", my_rank, n_dest);
+  ETB_CHECK_ARG(dest_offset >= 0, "dest_offset must be >= 0");
+  ETB_CHECK_ARG(epoch != 0, "epoch must not be 0");
+  ETB_CHECK_ARG(rows >= 0, "rows must be >= 0");
+  PeerOut peers{};
+  for (int i = 0; i < n_dest; ++i) {
+    ETB_CHECK_ARG(dest_buffers[i] != nullptr && arrive_marks[i] != nullptr,
+                  "dest_buffers[%d] or arrive_marks[%d] is null", i, i);
+    peers.ptr[i] = dest_buffers[i];
+    peers.arrive[i] = reinterpret_cast<unsigned long long*>(arrive_marks[i]);
+  }
+  peers.n = n_dest;
+  peers.offset = dest_offset;
+  peers.epoch = epoch;
+  peers.rank = my_rank;
+  peers.blocks_done = h->d_blocks_done;
+  if (rows > 0) {
+    etb200_error_t err = check_common(h, logits_device, dtype, rows, row_stride_elems, dest_buffers[0]);
+    if (err != ETB200_OK) return err;
+  }
+  DeviceGuard guard(h->device);
+  return sample_rows_device(
+      h, logits_device, dtype, rows, row_stride_elems,
+      reinterpret_cast<unsigned long long*>(rng_states_device), nullptr,
+      static_cast<cudaStream_t>(stream), peers);
+}
+
+etb200_error_t etb200_sampler_get_status(etb200_sampler_t* h, int32_t* out_status) {
+  ETB_CHECK_ARG(h != nullptr && out_status != nullptr, "null argument");
+  DeviceGuard guard(h->device);
+  int v = 0;
+  ETB_CUDA(cudaMemcpy(&v, h->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    const int zero = 0;
+    ETB_CUDA(cudaMemcpy(h->d_status, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  }
+  *out_status = v;
+  return ETB200_OK;
 }
 
 etb200_error_t etb200_sampler_sample_rows_host(

@@ -619,6 +619,41 @@ __device__ __forceinline__ void store_token(
   }
 }
 
+// Arrival barrier among the GPUs of a node at the end of a launch (see PeerOut). Every thread
+// of every block calls it once, after its last store_token. No kernel of one GPU waits for
+// another kernel of the same GPU; the wait for the other GPUs is limited (about a second),
+// after which the launch records kStatusPeerTimeout in *status and ends.
+constexpr unsigned kArriveSpinLimit = 1u << 21;
+
+__device__ __forceinline__ void peer_arrival_barrier(const PeerOut& peers, int* status) {
+  if (peers.epoch == 0ull) return;  // launch-uniform
+  __shared__ int is_last;
+  __threadfence_system();  // this thread's id stores are ordered before the block's arrival
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(peers.blocks_done, 1);
+    is_last = (prev == (int)gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!is_last) return;  // block-uniform
+  __threadfence_system();  // every block's ids before this rank's arrival marks
+  if (threadIdx.x == 0) *peers.blocks_done = 0;
+  if ((int)threadIdx.x < peers.n) {
+    volatile unsigned long long* theirs = peers.arrive[threadIdx.x] + peers.rank;
+    *theirs = peers.epoch;  // tell rank threadIdx.x that this rank's ids are in its buffer
+    volatile unsigned long long* mine = peers.arrive[peers.rank] + threadIdx.x;
+    unsigned spins = 0;
+    while (*mine < peers.epoch) {  // until rank threadIdx.x has told this rank
+      if (++spins > kArriveSpinLimit) {
+        atomicExch(status, kStatusPeerTimeout);
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+}
+
 // xorshift64* step and 24-bit coin of the reference (sampler.cpp:210-220).
 __device__ __forceinline__ float next_coin(unsigned long long* state) {
   unsigned long long s = *state;
@@ -1314,7 +1349,6 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     float topp, int topk, unsigned long long* __restrict__ rng_states,
     int64_t* __restrict__ out_ids, PeerOut peers, Entry* scratch, ExpTable table,
     int* __restrict__ status) {
-  (void)status;
   using S = Shared<kLut>;
   // the block's shared state exceeds the 48 KB static limit: dynamic shared memory, sized
   // sizeof(S) by the launcher
@@ -1629,6 +1663,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     store_token(out_ids, peers, r, token);
     __syncthreads();
   }
+  peer_arrival_barrier(peers, status);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1644,7 +1679,7 @@ constexpr int kArgVecs = 8;
 template <typename T, bool kRawU16>
 __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
-    int64_t* __restrict__ out_ids, PeerOut peers) {
+    int64_t* __restrict__ out_ids, PeerOut peers, int* __restrict__ status) {
   constexpr int kPerVec = 16 / sizeof(T);
   __shared__ float sv[kWarps];
   __shared__ int si[kWarps];
@@ -1741,6 +1776,7 @@ __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
     __syncthreads();
     store_token(out_ids, peers, r, __float_as_int(sv[0]));
   }
+  peer_arrival_barrier(peers, status);
 }
 
 __global__ void expf_selftest_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n,
@@ -1816,23 +1852,23 @@ cudaError_t launch_sample_rows(
 
 cudaError_t launch_argmax_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
-    const PeerOut& peers, int blocks, cudaStream_t stream) {
+    const PeerOut& peers, int blocks, int* status, cudaStream_t stream) {
   switch (dtype) {
     case kDtypeFloat:
       argmax_rows_kernel<float, false><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const float*>(logits), rows, vocab, row_stride, out_ids, peers);
+          static_cast<const float*>(logits), rows, vocab, row_stride, out_ids, peers, status);
       break;
     case kDtypeHalf:
       argmax_rows_kernel<__half, false><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const __half*>(logits), rows, vocab, row_stride, out_ids, peers);
+          static_cast<const __half*>(logits), rows, vocab, row_stride, out_ids, peers, status);
       break;
     case kDtypeBFloat16:
       argmax_rows_kernel<__nv_bfloat16, false><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, out_ids, peers);
+          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, out_ids, peers, status);
       break;
     case kDtypeUInt16:
       argmax_rows_kernel<unsigned short, true><<<blocks, kThreads, 0, stream>>>(
-          static_cast<const unsigned short*>(logits), rows, vocab, row_stride, out_ids, peers);
+          static_cast<const unsigned short*>(logits), rows, vocab, row_stride, out_ids, peers, status);
       break;
     default:
       return cudaErrorInvalidValue;

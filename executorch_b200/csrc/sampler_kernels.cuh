@@ -25,6 +25,15 @@ struct PeerOut {
   int64_t* ptr[kMaxPeers];
   int n;
   long long offset;
+  // Optional arrival barrier at the end of the launch (epoch != 0): arrive[p] is rank p's
+  // array of kMaxPeers 64-bit arrival marks. When the last block of this launch is done it
+  // writes `epoch` into arrive[p][rank] of every rank p and then waits, with a limit, until
+  // arrive[rank][q] >= epoch for every q: when the launch completes, this GPU's buffer holds
+  // the ids of all ranks. blocks_done is a counter of this GPU that is zero between launches.
+  unsigned long long* arrive[kMaxPeers];
+  unsigned long long epoch;
+  int rank;
+  int* blocks_done;
 };
 
 // Bytes of candidate-list scratch the sampling kernel needs when launched with `blocks`
@@ -47,7 +56,10 @@ cudaError_t launch_sample_rows(
 // temperature == 0: greedy argmax of every row.
 cudaError_t launch_argmax_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
-    const PeerOut& peers, int blocks, cudaStream_t stream);
+    const PeerOut& peers, int blocks, int* status, cudaStream_t stream);
+
+// Value stored into `status` when the arrival barrier of PeerOut gave up waiting for a rank.
+constexpr int kStatusPeerTimeout = 2;
 
 // y[i] = expf_ref(x[i]) on the device, for x <= 0: lets a test compare the device
 // exponential with the host libm.

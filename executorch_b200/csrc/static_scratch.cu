@@ -107,7 +107,7 @@ etb200_error_t etb200_sample_rows_static(
   if (inv_t == 0.0f) {
     const int64_t cap = (int64_t)sms * 4;
     e = launch_argmax_rows(dtype, logits_device, rows, vocab_size, row_stride_elems, out_ids_device,
-                           PeerOut{}, (int)(rows < cap ? rows : cap), st);
+                           PeerOut{}, (int)(rows < cap ? rows : cap), nullptr, st);
   } else {
     if (dtype == kDtypeUInt16)
       return fail(ETB200_NOT_SUPPORTED, "UInt16 logits can only be sampled at temperature 0");

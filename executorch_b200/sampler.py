@@ -162,6 +162,38 @@ class Sampler:
             self._h, C.c_void_p(logits.data_ptr()), _dtype_code(logits), rows, logits.stride(0),
             states_ptr, arr, len(dest_ptrs), dest_offset, self._stream()))
 
+    def sample_rows_exchange(self, logits: torch.Tensor, rng_states: torch.Tensor | None,
+                             dest_ptrs, mark_ptrs, rank: int, dest_offset: int, epoch: int) -> None:
+        """``sample_rows_scatter`` with the cross-GPU synchronisation inside the launch: when
+        the launch has completed, the buffer ``dest_ptrs[rank]`` holds the ids of all ranks.
+        ``mark_ptrs[p]`` is rank p's array of arrival marks; ``epoch`` grows by one per call on
+        every rank. ``logits`` may have zero rows."""
+        rows = logits.shape[0]
+        if rows:
+            self._check_rows(logits)
+        states_ptr = C.c_void_p(0)
+        if rng_states is not None and rows:
+            if (rng_states.dtype != torch.int64 or rng_states.numel() != rows
+                    or not rng_states.is_contiguous() or rng_states.device != self.device):
+                raise ValueError("rng_states must be a contiguous int64 device tensor, one per row")
+            states_ptr = C.c_void_p(rng_states.data_ptr())
+        if len(dest_ptrs) != len(mark_ptrs):
+            raise ValueError("one destination buffer and one mark array per rank")
+        dst = (C.c_void_p * len(dest_ptrs))(*[C.c_void_p(int(p)) for p in dest_ptrs])
+        marks = (C.c_void_p * len(mark_ptrs))(*[C.c_void_p(int(p)) for p in mark_ptrs])
+        _lib.check(_lib.load().etb200_sampler_sample_rows_exchange(
+            self._h, C.c_void_p(logits.data_ptr() if rows else 0), _dtype_code(logits), rows,
+            logits.stride(0) if rows else 0, states_ptr, dst, marks, len(dest_ptrs), rank, dest_offset,
+            epoch, self._stream()))
+
+    @property
+    def status(self) -> int:
+        """Reads and clears the device status word (synchronises): 0, or 2 after an arrival
+        wait of ``sample_rows_exchange`` ran out."""
+        v = C.c_int32(0)
+        _lib.check(_lib.load().etb200_sampler_get_status(self._h, C.byref(v)))
+        return int(v.value)
+
     def sample_rows_host(self, logits, rng_states: np.ndarray | None, dtype: str | None = None
                          ) -> np.ndarray:
         """Host-memory entry: ``logits`` is a [rows, vocab] CPU tensor or numpy array

@@ -22,24 +22,46 @@ def shard_rows(rows: int, rank: int, world: int) -> tuple[int, int]:
 
 class PeerIdExchange:
     """The id exchange without a collective call: one int64 buffer of ``total_rows`` per rank in
-    torch's symmetric memory (every rank can address every peer's copy over NVLink). The
-    sampling kernel's epilogue stores each id into all copies
-    (``Sampler.sample_rows_scatter``); ``finish()`` enqueues the barrier after which this
-    rank's copy holds the ids of all ranks. Ranks must be the GPUs of one node."""
+    torch's symmetric memory (every rank can address every peer's copy over NVLink), plus 16
+    arrival marks per rank. The sampling kernel's epilogue stores each id into all copies.
+    Two ways to synchronise the ranks afterwards:
+
+    * ``Sampler.sample_rows_scatter`` + ``finish()``: ``finish`` enqueues a symmetric-memory
+      barrier after which this rank's copy holds the ids of all ranks;
+    * ``Sampler.sample_rows_exchange`` with ``mark_ptrs`` and ``next_epoch()``: the last block
+      of the launch marks its arrival at every rank and waits (with a limit) for theirs, so
+      the launch itself ends with a complete buffer and ``finish(barrier=False)`` only
+      returns it.
+
+    Ranks must be the GPUs of one node."""
 
     def __init__(self, total_rows: int, device, group=None):
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group if group is not None else dist.group.WORLD
-        self.buffer = symm_mem.empty(total_rows, dtype=torch.int64, device=device)
-        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.rank = dist.get_rank(self.group)
+        # ids and arrival marks live in one symmetric allocation: [total_rows ids | 16 marks]
+        self.storage = symm_mem.empty(total_rows + 16, dtype=torch.int64, device=device)
+        self.storage.zero_()
+        self.handle = symm_mem.rendezvous(self.storage, self.group)
+        self.buffer = self.storage[:total_rows]
         self.dest_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.mark_ptrs = [int(p) + 8 * total_rows for p in self.handle.buffer_ptrs]
         if len(self.dest_ptrs) > 16:
             raise ValueError("at most 16 ranks can exchange ids through peer buffers")
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        self.handle.barrier(channel=0)  # every rank's marks are zero before anyone writes one
+        torch.cuda.synchronize(device)
 
-    def finish(self) -> torch.Tensor:
-        # all ranks' stores are ordered before the barrier's release on each stream
-        self.handle.barrier(channel=0)
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def finish(self, barrier: bool = True) -> torch.Tensor:
+        if barrier:
+            # all ranks' stores are ordered before the barrier's release on each stream
+            self.handle.barrier(channel=0)
         return self.buffer
 
 
@@ -50,10 +72,12 @@ class ShardedSampler:
     tests inject a CPU stand-in to exercise the exchange with the gloo backend."""
 
     def __init__(self, local_sample: Callable[[torch.Tensor, torch.Tensor | None], torch.Tensor],
-                 total_rows: int, group=None, scatter=None, device=None):
+                 total_rows: int, group=None, scatter=None, device=None, in_kernel_sync: bool = False):
         """``scatter(logits, rng_states, dest_ptrs, dest_offset)`` (normally
         ``Sampler.sample_rows_scatter``) selects the peer-buffer exchange instead of the
-        all-gather; it needs equal shards and a CUDA ``device``."""
+        all-gather; it needs equal shards and a CUDA ``device``. With ``in_kernel_sync`` the
+        callable is ``Sampler.sample_rows_exchange`` and the ranks synchronise inside the
+        sampling launch instead of through a barrier behind it."""
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.local_sample = local_sample
@@ -64,6 +88,7 @@ class ShardedSampler:
         self.start, self.count = shard_rows(total_rows, self.rank, self.world)
         self.even = total_rows % self.world == 0
         self.scatter = scatter
+        self.in_kernel_sync = in_kernel_sync
         self.exchange = None
         if scatter is not None:
             if not self.even:
@@ -75,6 +100,11 @@ class ShardedSampler:
         if local_logits.shape[0] != self.count:
             raise ValueError(f"rank {self.rank} owns {self.count} rows, got {local_logits.shape[0]}")
         if self.exchange is not None:
+            if self.in_kernel_sync:
+                ex = self.exchange
+                self.scatter(local_logits, local_states, ex.dest_ptrs, ex.mark_ptrs, ex.rank, self.start,
+                             ex.next_epoch())
+                return ex.finish(barrier=False)
             self.scatter(local_logits, local_states, self.exchange.dest_ptrs, self.start)
             return self.exchange.finish()
         ids = self.local_sample(local_logits, local_states)

@@ -129,6 +129,28 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_scatter(
     int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,
     int32_t n_dest, int64_t dest_offset, void* stream);
 
+/* etb200_sampler_sample_rows_scatter with the cross-GPU synchronisation inside the same
+ * launch (no counterpart in the reference). arrive_marks is a HOST array of n_dest device
+ * pointers: arrive_marks[p] is an array of at least n_dest uint64 in rank p's memory that
+ * every rank can address (symmetric / peer-mapped memory), zero before the first call. When
+ * the last thread block of this launch has stored its ids, it writes `epoch` into
+ * arrive_marks[p][my_rank] for every p and then waits until arrive_marks[my_rank][q] >= epoch
+ * for every q: once the launch has completed on `stream`, this rank's buffer holds the ids
+ * of all ranks for this epoch. Every rank must make the call with the same epoch, which must
+ * grow from call to call (1, 2, 3, ...); a rank with rows == 0 still calls. The wait is
+ * limited to about a second; if it runs out the launch ends and etb200_sampler_get_status
+ * reports 2 (ids of the missing ranks are then stale). Ranks must be distinct GPUs: two such
+ * launches never wait for each other on one GPU. */
+ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_exchange(
+    etb200_sampler_t* handle, const void* logits_device, int32_t dtype, int64_t rows,
+    int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,
+    uint64_t* const* arrive_marks, int32_t n_dest, int32_t my_rank, int64_t dest_offset,
+    uint64_t epoch, void* stream);
+
+/* Reads and clears the handle's device status word (synchronises): 0 = nothing to report,
+ * 2 = the arrival wait of etb200_sampler_sample_rows_exchange ran out for some rank. */
+ETB200_EXPORT etb200_error_t etb200_sampler_get_status(etb200_sampler_t* handle, int32_t* out_status);
+
 /* Same as etb200_sampler_sample_rows for callers whose logits live in HOST memory (what
  * sample_from_logits receives from a CPU tensor, util.h:25-55): copies the rows to the
  * device, samples, copies ids and advanced states back, and synchronises the stream.

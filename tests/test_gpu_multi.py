@@ -1,5 +1,6 @@
-"""Row sharding across the GPUs of one node, with real samplers: both id exchanges (NCCL
-all-gather, and ids stored into the peers' buffers by the kernel epilogue) must leave every
+"""Row sharding across the GPUs of one node, with real samplers: the id exchanges (NCCL
+all-gather; ids stored into the peers' buffers by the kernel epilogue, synchronised by a
+barrier behind the launch or by arrival marks inside it) must leave every
 rank with the tokens a single GPU would produce. Runs only where at least two GPUs are
 visible; ranks leave together, between steps."""
 import os
@@ -32,9 +33,10 @@ def _worker(rank, world, port, q):
         want = oracle.Restatement().sample_rows(x, 0.7, 0.9, seeds, dtype="bf16", threads=2)
         s = Sampler(vocab, 0.7, 0.9, 0, device=dev)
         ok = True
-        for mode in ("nccl", "p2p"):
-            sh = ShardedSampler(s.sample_rows, total, scatter=s.sample_rows_scatter if mode == "p2p" else None,
-                                device=dev)
+        for mode in ("nccl", "p2p", "p2p-in-kernel"):
+            scatter = {"nccl": None, "p2p": s.sample_rows_scatter, "p2p-in-kernel": s.sample_rows_exchange}[mode]
+            sh = ShardedSampler(s.sample_rows, total, scatter=scatter, device=dev,
+                                in_kernel_sync=mode == "p2p-in-kernel")
             lo, n = sh.start, sh.count
             t = torch.from_numpy(x[lo:lo + n].view(np.int16)).to(dev).view(torch.bfloat16)
             for _ in range(3):  # repeated steps reuse the exchange buffer
@@ -42,6 +44,7 @@ def _worker(rank, world, port, q):
                 torch.cuda.synchronize()
                 ok = ok and np.array_equal(ids.cpu().numpy(), want)
             dist.barrier()
+        ok = ok and s.status == 0  # no arrival wait ran out
         s.close()
         q.put((rank, ok))
     finally:
