@@ -3,7 +3,7 @@
 
 __all__ = ["Sampler", "sample_from_logits", "sample_all_from_logits", "logits_to_token",
            "seeds_to_states", "ShardedSampler", "shard_rows", "LogitProcessor",
-           "apply_logit_processors", "TokenGenerator"]
+           "apply_logit_processors", "TokenGenerator", "Stats"]
 
 
 def __getattr__(name):
@@ -14,7 +14,7 @@ def __getattr__(name):
     if name in ("ShardedSampler", "shard_rows"):
         from . import sharded
         return getattr(sharded, name)
-    if name in ("LogitProcessor", "apply_logit_processors", "TokenGenerator"):
+    if name in ("LogitProcessor", "apply_logit_processors", "TokenGenerator", "Stats"):
         from . import generator
         return getattr(generator, name)
     raise AttributeError(name)

@@ -5,7 +5,9 @@ import numpy as np
 import pytest
 import torch
 
-from executorch_b200 import (LogitProcessor, Sampler, TokenGenerator, _lib, apply_logit_processors,
+import json
+
+from executorch_b200 import (LogitProcessor, Sampler, Stats, TokenGenerator, _lib, apply_logit_processors,
                              logits_to_token)
 
 pytestmark = pytest.mark.gpu
@@ -97,6 +99,34 @@ def test_generate_calls_back_once_per_token_and_counts_steps(cuda_device):
     seen = []
     n = g.generate([1, 2, 3], start_pos=3, max_new_tokens=10, temperature=0.0, token_callback=seen.append)
     assert n == 10 and len(seen) == 10 and model.calls == 10 and set(seen) == {"3"}
+    s.close()
+
+
+def test_generate_fills_the_reference_stats_and_report_line(cuda_device):
+    """The counters a decode loop feeds in the reference's Stats (stats.h:24-75) and the
+    JSON keys of its PyTorchObserver line (stats.h:113-165)."""
+    model = FakeModel(torch.tensor([[0.1, 0.2, 0.3, 0.4]], device=cuda_device))
+    s = Sampler(4, 0.5, 0.9, 3, device=cuda_device)
+    st = Stats()
+    g = TokenGenerator(model, s, stats=st)
+    n = g.generate([5, 6], start_pos=2, max_new_tokens=7, temperature=0.5)
+    assert n == 7 and st.num_generated_tokens == 7 and st.num_prompt_tokens == 2
+    assert st.aggregate_sampling_time_ms > 0 and g.sampling_time_ms == st.aggregate_sampling_time_ms
+    assert st.aggregate_model_execution_time_ms > 0
+    assert 0 < st.inference_start_ms <= st.first_token_ms <= st.inference_end_ms
+    line = st.report_line()
+    assert line.startswith("PyTorchObserver {")
+    d = json.loads(line[len("PyTorchObserver "):])
+    keys = list(d)
+    assert keys[-1] == "SCALING_FACTOR_UNITS_PER_SECOND" and d[keys[-1]] == 1000
+    for k in ("prompt_tokens", "generated_tokens", "model_load_start_ms", "model_load_end_ms",
+              "inference_start_ms", "inference_end_ms", "model_execution_start_ms",
+              "model_execution_end_ms", "prompt_eval_end_ms", "first_token_ms",
+              "aggregate_sampling_time_ms", "aggregate_model_execution_time_ms"):
+        assert k in d
+    assert d["generated_tokens"] == 7
+    st.reset()
+    assert st.num_generated_tokens == 0 and st.aggregate_sampling_time_ms == 0
     s.close()
 
 
