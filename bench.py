@@ -39,6 +39,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes (read + write) of ONE launch of the sampling kernel on the benchmark batch, from
 # the ncu capture whose summary is kept under profiles/.
+NCU_DRAM_BYTES_GREEDY = 65_930_000  # 65.68 MB read + 0.25 MB written (mean of two captured launches)
 NCU_DRAM_BYTES_PER_LAUNCH = 67_100_000  # 65.9 MB read + 1.2 MB written (mean of two captured launches)
 
 
@@ -176,6 +177,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--greedy", action="store_true",
+                    help="config 3's second pass instead of the headline: temperature 0 (argmax) on the same batch")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-in-kernel", "nccl"],
                     help="N > 1: ids stored into the peers' buffers by the kernel, ranks synchronised by a barrier "
                          "behind the launch (p2p) or by arrival marks inside it (p2p-in-kernel); or all-gathered (nccl)")
@@ -215,7 +218,9 @@ def main():
     states = states0.clone()
     local_ids = torch.empty(rows, dtype=torch.int64, device=dev)
     all_ids = torch.empty(total_rows, dtype=torch.int64, device=dev) if world > 1 else local_ids
-    sampler = Sampler(vocab, cfg.temperature, cfg.topp, 0, device=dev)
+    sampler = Sampler(vocab, 0.0 if args.greedy else cfg.temperature, cfg.topp, 0, device=dev)
+    if args.greedy:
+        args.no_cpu_baseline = True
 
     exchange, exchange_name = None, "none"
     if world > 1:
@@ -325,17 +330,20 @@ def main():
         algo_bytes = rows * (vocab * 2 + 8 + 16)  # logits once + id + rng state in/out
         achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+            "metric": "argmax_rows_per_s_v128256_bf16" if args.greedy else METRIC,
+            "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": "c3: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0.7, top-p 0.95, seed=row",
+                "workload": ("c3 second pass: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0 (argmax)" if args.greedy
+                             else "c3: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0.7, top-p 0.95, seed=row"),
                 "rows_per_gpu": rows, "vocab": vocab, "global_rows": total_rows,
                 "l2": f"{NBUF} rotating input batches ({NBUF * rows * vocab * 2 / 1e6:.0f} MB > 126 MB L2)",
                 "exchange": exchange_name,
             },
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "frac": achieved / peak,
+                         "traffic": NCU_DRAM_BYTES_GREEDY if args.greedy else NCU_DRAM_BYTES_PER_LAUNCH,
                          "peak_source": f"of {which}", "kernel_ms": kernel_ms,
                          "algorithmic_bytes_per_launch": algo_bytes},
             "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": h2d,
