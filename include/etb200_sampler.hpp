@@ -159,6 +159,31 @@ class Sampler {
         stream));
   }
 
+  // Multi-GPU forms (no counterpart in the reference): the id of row r goes to index
+  // dest_offset + r of every buffer in dest_buffers (this GPU's and its peers'); the second form
+  // also synchronises the ranks inside the launch (see etb200_sampler_sample_rows_exchange).
+  Error sample_rows_scatter(const void* logits, ScalarType dtype, int64_t rows, int64_t row_stride_elems,
+                            uint64_t* rng_states, int64_t* const* dest_buffers, int32_t n_dest,
+                            int64_t dest_offset, void* stream = nullptr) {
+    return static_cast<Error>(etb200_sampler_sample_rows_scatter(
+        handle_, logits, static_cast<int32_t>(dtype), rows, row_stride_elems, rng_states, dest_buffers,
+        n_dest, dest_offset, stream));
+  }
+  Error sample_rows_exchange(const void* logits, ScalarType dtype, int64_t rows, int64_t row_stride_elems,
+                             uint64_t* rng_states, int64_t* const* dest_buffers,
+                             uint64_t* const* arrive_marks, int32_t n_dest, int32_t my_rank,
+                             int64_t dest_offset, uint64_t epoch, void* stream = nullptr) {
+    return static_cast<Error>(etb200_sampler_sample_rows_exchange(
+        handle_, logits, static_cast<int32_t>(dtype), rows, row_stride_elems, rng_states, dest_buffers,
+        arrive_marks, n_dest, my_rank, dest_offset, epoch, stream));
+  }
+  // Reads and clears the device status word: 0, or 2 after an arrival wait ran out.
+  int32_t device_status() {
+    int32_t v = 0;
+    etb200_sampler_get_status(handle_, &v);
+    return v;
+  }
+
   // Sampler::rng_state_ (sampler.h:82), for checkpoint and resume.
   unsigned long long rng_state() const {
     uint64_t s = 0;
