@@ -43,6 +43,12 @@ struct etb200_sampler {
   uint64_t launches = 0;
   int blocks_per_sm[3] = {0, 0, 0};  // occupancy of the sampling kernel per dtype, queried once
   ExpTable table;
+  // Rows that the cluster kernel leaves undecided: [0], [1] are the counters of alternating
+  // launches (each launch clears the other one), [2...] the row numbers.
+  int* d_retry = nullptr;
+  int64_t retry_cap = 0;
+  unsigned retry_parity = 0;
+  int kernel_choice = 0;  // 0: cluster kernel where it applies; 1: always the one-block-per-row kernel
 };
 
 namespace {
@@ -165,6 +171,23 @@ int grid_blocks(etb200_sampler* h, int dtype, int64_t rows) {
   return (int)(rows < resident ? rows : resident);
 }
 
+etb200_error_t ensure_retry_list(etb200_sampler* h, int64_t rows) {
+  if (rows <= h->retry_cap) return ETB200_OK;
+  if (h->d_retry) {
+    ETB_CUDA(cudaDeviceSynchronize());
+    ETB_CUDA(cudaFree(h->d_retry));
+    h->d_retry = nullptr;
+    h->retry_cap = 0;
+  }
+  const size_t bytes = sizeof(int) * (size_t)(rows + 2);
+  cudaError_t e = cudaMalloc(&h->d_retry, bytes);
+  if (e != cudaSuccess)
+    return fail(ETB200_MEMORY_ALLOCATION_FAILED, "cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+  ETB_CUDA(cudaMemset(h->d_retry, 0, 2 * sizeof(int)));
+  h->retry_cap = rows;
+  return ETB200_OK;
+}
+
 etb200_error_t ensure_scratch(etb200_sampler* h, int blocks) {
   const size_t need = sampler_scratch_bytes(h->vocab, blocks);
   if (need <= h->scratch_bytes) return ETB200_OK;
@@ -214,6 +237,25 @@ etb200_error_t sample_rows_device(
     etb200_error_t err = ensure_scratch(h, blocks);
     if (err != ETB200_OK) return err;
   }
+  if (h->kernel_choice == 0 &&
+      topp_cluster_supported(dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk)) {
+    // Fast path: one thread-block cluster per row. Rows it leaves undecided (rare) are then
+    // sampled by the one-block-per-row kernel, which also carries the arrival barrier.
+    etb200_error_t err = ensure_retry_list(h, rows);
+    if (err != ETB200_OK) return err;
+    int* count = h->d_retry + (h->retry_parity & 1u);
+    int* count_next = h->d_retry + ((h->retry_parity + 1u) & 1u);
+    h->retry_parity += 1u;
+    PeerOut no_barrier = peers;
+    no_barrier.epoch = 0ull;
+    ETB_CUDA(launch_topp_cluster(logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, rng_states,
+                                 out_ids, no_barrier, h->table, h->d_retry + 2, count, count_next, stream));
+    ETB_CUDA(launch_sample_rows(
+        dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk, rng_states,
+        out_ids, peers, h->scratch, blocks, h->table, h->d_status, stream, h->d_retry + 2, count));
+    h->launches += 2;
+    return ETB200_OK;
+  }
   ETB_CUDA(launch_sample_rows(
       dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk, rng_states,
       out_ids, peers, h->scratch, blocks, h->table, h->d_status, stream));
@@ -261,6 +303,7 @@ etb200_error_t etb200_sampler_destroy(etb200_sampler_t* h) {
   cudaFreeHost(h->h_token);
   cudaFree(h->d_status);
   cudaFree(h->scratch);
+  cudaFree(h->d_retry);
   cudaFree(h->d_stage);
   cudaFree(h->d_stage_states);
   cudaFree(h->d_stage_ids);
@@ -282,6 +325,24 @@ etb200_error_t etb200_sampler_set_temperature(etb200_sampler_t* h, float tempera
 etb200_error_t etb200_sampler_set_topk(etb200_sampler_t* h, int32_t topk) {
   ETB_CHECK_ARG(h != nullptr, "handle is null");
   h->topk = topk;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_set_kernel_choice(etb200_sampler_t* h, int32_t choice) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  ETB_CHECK_ARG(choice == 0 || choice == 1, "choice must be 0 (automatic) or 1 (one block per row), got %d", choice);
+  h->kernel_choice = choice;
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_last_retry_count(etb200_sampler_t* h, int32_t* out_count) {
+  ETB_CHECK_ARG(h != nullptr && out_count != nullptr, "null argument");
+  *out_count = 0;
+  if (h->d_retry == nullptr || h->retry_parity == 0u) return ETB200_OK;
+  DeviceGuard guard(h->device);
+  int v = 0;
+  ETB_CUDA(cudaMemcpy(&v, h->d_retry + ((h->retry_parity - 1u) & 1u), sizeof(int), cudaMemcpyDeviceToHost));
+  *out_count = v;
   return ETB200_OK;
 }
 

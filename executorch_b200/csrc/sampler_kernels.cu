@@ -19,6 +19,7 @@
 //
 // The candidate lists of 3b live in global scratch memory owned by the caller of the launch
 // functions (two buffers of vocab entries per resident block).
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -26,6 +27,7 @@
 
 #include <type_traits>
 
+#include "cluster_math.cuh"
 #include "exact_math.cuh"
 #include "sampler_kernels.cuh"
 
@@ -1348,7 +1350,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
     float topp, int topk, unsigned long long* __restrict__ rng_states,
     int64_t* __restrict__ out_ids, PeerOut peers, Entry* scratch, ExpTable table,
-    int* __restrict__ status) {
+    int* __restrict__ status, const int* __restrict__ row_list, const int* __restrict__ row_count) {
   using S = Shared<kLut>;
   // the block's shared state exceeds the 48 KB static limit: dynamic shared memory, sized
   // sizeof(S) by the launcher
@@ -1369,7 +1371,10 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   Entry* listA = scratch + (size_t)blockIdx.x * 2 * (size_t)vocab;
   Entry* listB = listA + vocab;
 
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+  // with a row list (rows that the cluster kernel left undecided) only those rows are sampled
+  const int64_t n_todo = row_list != nullptr ? (int64_t)*row_count : rows;
+  for (int64_t it = blockIdx.x; it < n_todo; it += gridDim.x) {
+    const int64_t r = row_list != nullptr ? (int64_t)row_list[it] : it;
     RowMath<T, S> rm;
     rm.row = logits + r * row_stride;
     rm.vocab = vocab;
@@ -1779,6 +1784,8 @@ __global__ void __launch_bounds__(kThreads, 2) argmax_rows_kernel(
   peer_arrival_barrier(peers, status);
 }
 
+#include "cluster_topp.cuh"
+
 __global__ void expf_selftest_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n,
                                      ExpTable table) {
   __shared__ uint64_t tab[kExpTableSize];
@@ -1819,35 +1826,81 @@ template <typename T, bool kLut>
 static cudaError_t launch_sample_t(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
     int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, void* scratch,
-    int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
+    int blocks, const ExpTable& table, int* status, const int* row_list, const int* row_count,
+    cudaStream_t stream) {
   const cudaError_t attr = prepare_sample_kernel<T, kLut>();
   if (attr != cudaSuccess) return attr;
   sample_rows_kernel<T, kLut><<<blocks, kThreads, sizeof(Shared<kLut>), stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       peers,
-      static_cast<Entry*>(scratch), table, status);
+      static_cast<Entry*>(scratch), table, status, row_list, row_count);
   return cudaGetLastError();
 }
 
 cudaError_t launch_sample_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
     float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers,
-    void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
+    void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream,
+    const int* row_list, const int* row_count) {
   switch (dtype) {
     case kDtypeFloat:
       return launch_sample_t<float, false>(logits, rows, vocab, row_stride, inv_t, topp, topk,
-                                           rng_states, out_ids, peers, scratch, blocks, table, status, stream);
+                                           rng_states, out_ids, peers, scratch, blocks, table, status,
+                                           row_list, row_count, stream);
     case kDtypeHalf:
       return launch_sample_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp, topk,
                                             rng_states, out_ids, peers, scratch, blocks, table, status,
-                                            stream);
+                                            row_list, row_count, stream);
     case kDtypeBFloat16:
       return launch_sample_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp, topk,
                                                   rng_states, out_ids, peers, scratch, blocks, table,
-                                                  status, stream);
+                                                  status, row_list, row_count, stream);
     default:
       return cudaErrorInvalidValue;
   }
+}
+
+bool topp_cluster_supported(int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride,
+                            float inv_t, float topp, int topk) {
+  if (dtype != kDtypeBFloat16 || !(inv_t > 0.0f) || topk > 0) return false;
+  if (!(topp > 0.0f && topp < 1.0f)) return false;
+  if (vocab < kClusterMinVocab || vocab > kCMaxCluster * kCSliceMax) return false;
+  if (rows < 1 || rows > (int64_t)0x7fffffff / kCMaxCluster) return false;
+  // every row must start on a 16-byte boundary (bulk copies)
+  if ((reinterpret_cast<uintptr_t>(logits) & 15u) != 0) return false;
+  if (rows > 1 && ((row_stride * 2) & 15) != 0) return false;
+  return true;
+}
+
+cudaError_t launch_topp_cluster(
+    const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
+    unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, const ExpTable& table,
+    int* retry_rows, int* retry_count, int* retry_count_next, cudaStream_t stream) {
+  int csize = 1;
+  while (csize * kCSliceMax < vocab) csize *= 2;
+  const int slice_len = ((vocab + csize * kCTerms - 1) / (csize * kCTerms)) * kCTerms;
+  cudaError_t e = cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)sizeof(ClusterShared));
+  if (e != cudaSuccess) return e;
+  if (csize > 8) {
+    e = cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(rows * csize), 1, 1);
+  cfg.blockDim = dim3(kCThreads, 1, 1);
+  cfg.dynamicSmemBytes = sizeof(ClusterShared);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, topp_cluster_kernel, static_cast<const unsigned short*>(logits), rows,
+                            vocab, row_stride, slice_len, inv_t, topp, rng_states, out_ids, peers, table,
+                            retry_rows, retry_count, retry_count_next);
 }
 
 cudaError_t launch_argmax_rows(

@@ -47,11 +47,26 @@ int sampler_threads();
 
 // temperature != 0: top-k (0 < topk < vocab), else multinomial (topp outside (0,1)) or top-p
 // sampling of every row. rng_states[r] is advanced once per row; out_ids[r] receives the
-// token. Top-k and top-p need `scratch` (sampler_scratch_bytes).
+// token. Top-k and top-p need `scratch` (sampler_scratch_bytes). With row_list, only the
+// *row_count rows it names are sampled (both are device pointers).
 cudaError_t launch_sample_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
     float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers,
-    void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream);
+    void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream,
+    const int* row_list = nullptr, const int* row_count = nullptr);
+
+// Top-p sampling of bf16 rows with one thread-block cluster per row (the fast path). Rows it
+// cannot decide are appended to retry_rows (their count in *retry_count) with their rng state
+// and output untouched; the caller then runs launch_sample_rows with that list on the same
+// stream. *retry_count must be zero when the kernel starts; the kernel clears
+// *retry_count_next for the launch after it.
+constexpr int kClusterMinVocab = 256;
+bool topp_cluster_supported(int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride,
+                            float inv_t, float topp, int topk);
+cudaError_t launch_topp_cluster(
+    const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
+    unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, const ExpTable& table,
+    int* retry_rows, int* retry_count, int* retry_count_next, cudaStream_t stream);
 
 // temperature == 0: greedy argmax of every row.
 cudaError_t launch_argmax_rows(

@@ -80,6 +80,11 @@ class Sampler:
     def set_topk(self, topk: int) -> None:
         _lib.check(_lib.load().etb200_sampler_set_topk(self._h, topk))
 
+    def set_kernel_choice(self, choice: int) -> None:
+        """0: the cluster-per-row top-p kernel where it applies (default); 1: always the
+        one-block-per-row kernel. Both return the same tokens."""
+        _lib.check(_lib.load().etb200_sampler_set_kernel_choice(self._h, choice))
+
     @property
     def rng_state(self) -> int:
         out = C.c_uint64(0)
@@ -89,6 +94,14 @@ class Sampler:
     @rng_state.setter
     def rng_state(self, value: int) -> None:
         _lib.check(_lib.load().etb200_sampler_set_rng_state(self._h, C.c_uint64(value & (2**64 - 1))))
+
+    @property
+    def last_retry_count(self) -> int:
+        """Rows of the most recent top-p call that the cluster kernel handed to the
+        one-block-per-row kernel (synchronises)."""
+        out = C.c_int32(0)
+        _lib.check(_lib.load().etb200_sampler_last_retry_count(self._h, C.byref(out)))
+        return int(out.value)
 
     @property
     def launch_count(self) -> int:

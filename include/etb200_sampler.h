@@ -191,6 +191,18 @@ ETB200_EXPORT const char* etb200_static_last_error_message(void);
 ETB200_EXPORT etb200_error_t etb200_selftest_expf(
     const float* x_device, float* y_device, int64_t n, void* stream);
 
+/* Which top-p kernel a handle uses (a tuning and testing knob; no counterpart in the
+ * reference). 0 (default): bf16 rows whose starts are 16-byte aligned, with 256 <= vocab_size
+ * <= 262144, temperature > 0 and no top-k, are sampled by the kernel that gives every row a
+ * thread-block cluster; any row it cannot decide, and every other case, goes to the kernel
+ * that gives every row one thread block. 1: always the latter. Both return the same tokens. */
+ETB200_EXPORT etb200_error_t etb200_sampler_set_kernel_choice(etb200_sampler_t* handle, int32_t choice);
+
+/* Diagnostic (synchronises the device): how many rows of the handle's most recent top-p call
+ * the cluster kernel left undecided and handed to the one-block-per-row kernel. 0 when the
+ * cluster kernel was not used. */
+ETB200_EXPORT etb200_error_t etb200_sampler_last_retry_count(etb200_sampler_t* handle, int32_t* out_count);
+
 /* Number of kernels this library has launched through `handle` so far. */
 ETB200_EXPORT etb200_error_t etb200_sampler_launch_count(
     etb200_sampler_t* handle, uint64_t* out_count);
