@@ -49,6 +49,7 @@ SYMBOLS = {
                                                C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "etb200_static_last_error_message": (C.c_char_p, []),
     "etb200_selftest_expf": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "etb200_sampler_set_wait_limit_ns": (C.c_uint32, [C.c_void_p, C.c_uint64]),
     "etb200_sampler_set_kernel_choice": (C.c_uint32, [C.c_void_p, C.c_int32]),
     "etb200_sampler_last_retry_count": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_int32)]),
     "etb200_sampler_launch_count": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_uint64)]),

@@ -47,8 +47,14 @@ struct etb200_sampler {
   // launches (each launch clears the other one), [2...] the row numbers.
   int* d_retry = nullptr;
   int64_t retry_cap = 0;
+  void* cluster_scratch = nullptr;  // per-row record lists of the cluster kernel, one batch of rows
+  size_t cluster_scratch_bytes = 0;
   unsigned retry_parity = 0;
-  int kernel_choice = 0;  // 0: cluster kernel where it applies; 1: always the one-block-per-row kernel
+  unsigned long long wait_ns = 1000000000ull;  // limit of the in-kernel wait for the other ranks
+  // 0: the estimate-guided variant for 16-bit logits; 1: always the variant without it;
+  // 2: the cluster-per-row kernels where they apply, else as 0
+  int kernel_choice = 0;
+  int guided_blocks_per_sm[2] = {0, 0};
 };
 
 namespace {
@@ -188,6 +194,27 @@ etb200_error_t ensure_retry_list(etb200_sampler* h, int64_t rows) {
   return ETB200_OK;
 }
 
+// Rows per launch of the cluster kernel pair: bounds the record scratch (about 110 KB per row
+// at a 128k vocabulary).
+constexpr int64_t kClusterBatchRows = 1024;
+
+etb200_error_t ensure_cluster_scratch(etb200_sampler* h, int64_t batch_rows) {
+  const size_t need = topp_cluster_scratch_bytes(h->vocab, batch_rows);
+  if (need <= h->cluster_scratch_bytes) return ETB200_OK;
+  if (h->cluster_scratch) {
+    ETB_CUDA(cudaDeviceSynchronize());
+    ETB_CUDA(cudaFree(h->cluster_scratch));
+    h->cluster_scratch = nullptr;
+    h->cluster_scratch_bytes = 0;
+  }
+  cudaError_t e = cudaMalloc(&h->cluster_scratch, need);
+  if (e != cudaSuccess)
+    return fail(ETB200_MEMORY_ALLOCATION_FAILED, "cudaMalloc of %zu scratch bytes failed: %s", need,
+                cudaGetErrorString(e));
+  h->cluster_scratch_bytes = need;
+  return ETB200_OK;
+}
+
 etb200_error_t ensure_scratch(etb200_sampler* h, int blocks) {
   const size_t need = sampler_scratch_bytes(h->vocab, blocks);
   if (need <= h->scratch_bytes) return ETB200_OK;
@@ -237,10 +264,14 @@ etb200_error_t sample_rows_device(
     etb200_error_t err = ensure_scratch(h, blocks);
     if (err != ETB200_OK) return err;
   }
-  if (h->kernel_choice == 0 &&
-      topp_cluster_supported(dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk)) {
-    // Fast path: one thread-block cluster per row. Rows it leaves undecided (rare) are then
-    // sampled by the one-block-per-row kernel, which also carries the arrival barrier.
+  const bool want_cluster = h->kernel_choice == 2 &&
+                            topp_cluster_supported(dtype, logits, rows, h->vocab, row_stride, h->inv_temperature,
+                                                   h->topp, topk);
+  const bool want_guided = !want_cluster && h->kernel_choice != 1 && guided_supported(dtype);
+  if (want_cluster || want_guided) {
+    // Two launches: the fast kernel(s) take every row; the rows they leave undecided (rare) are
+    // then sampled by the plain one-block-per-row kernel, which also carries the arrival
+    // barrier of the multi-GPU forms.
     etb200_error_t err = ensure_retry_list(h, rows);
     if (err != ETB200_OK) return err;
     int* count = h->d_retry + (h->retry_parity & 1u);
@@ -248,12 +279,32 @@ etb200_error_t sample_rows_device(
     h->retry_parity += 1u;
     PeerOut no_barrier = peers;
     no_barrier.epoch = 0ull;
-    ETB_CUDA(launch_topp_cluster(logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, rng_states,
-                                 out_ids, no_barrier, h->table, h->d_retry + 2, count, count_next, stream));
+    if (want_cluster) {
+      const int64_t batch = rows < kClusterBatchRows ? rows : kClusterBatchRows;
+      err = ensure_cluster_scratch(h, batch);
+      if (err != ETB200_OK) return err;
+      ETB_CUDA(launch_topp_cluster(logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, rng_states,
+                                   out_ids, no_barrier, h->table, h->cluster_scratch, batch, h->d_retry + 2,
+                                   count, count_next, stream));
+      h->launches += 2 * (uint64_t)((rows + batch - 1) / batch);
+    } else {
+      const int slot = dtype == kDtypeHalf ? 0 : 1;
+      if (h->guided_blocks_per_sm[slot] == 0) h->guided_blocks_per_sm[slot] = guided_kernel_max_blocks_per_sm(dtype);
+      const int64_t resident = (int64_t)h->sm_count * h->guided_blocks_per_sm[slot];
+      const int gblocks = (int)(rows < resident ? rows : resident);
+      if (gblocks > blocks) {
+        err = ensure_scratch(h, gblocks);
+        if (err != ETB200_OK) return err;
+      }
+      ETB_CUDA(launch_sample_rows_guided(dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp,
+                                         topk, rng_states, out_ids, no_barrier, h->scratch, gblocks, h->table,
+                                         h->d_status, h->d_retry + 2, count, count_next, stream));
+      h->launches += 1;
+    }
     ETB_CUDA(launch_sample_rows(
         dtype, logits, rows, h->vocab, row_stride, h->inv_temperature, h->topp, topk, rng_states,
         out_ids, peers, h->scratch, blocks, h->table, h->d_status, stream, h->d_retry + 2, count));
-    h->launches += 2;
+    h->launches += 1;
     return ETB200_OK;
   }
   ETB_CUDA(launch_sample_rows(
@@ -304,6 +355,7 @@ etb200_error_t etb200_sampler_destroy(etb200_sampler_t* h) {
   cudaFree(h->d_status);
   cudaFree(h->scratch);
   cudaFree(h->d_retry);
+  cudaFree(h->cluster_scratch);
   cudaFree(h->d_stage);
   cudaFree(h->d_stage_states);
   cudaFree(h->d_stage_ids);
@@ -328,9 +380,17 @@ etb200_error_t etb200_sampler_set_topk(etb200_sampler_t* h, int32_t topk) {
   return ETB200_OK;
 }
 
+etb200_error_t etb200_sampler_set_wait_limit_ns(etb200_sampler_t* h, uint64_t nanoseconds) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  ETB_CHECK_ARG(nanoseconds >= 1000ull && nanoseconds <= 60000000000ull,
+                "the wait limit must be between 1 microsecond and 60 seconds");
+  h->wait_ns = nanoseconds;
+  return ETB200_OK;
+}
+
 etb200_error_t etb200_sampler_set_kernel_choice(etb200_sampler_t* h, int32_t choice) {
   ETB_CHECK_ARG(h != nullptr, "handle is null");
-  ETB_CHECK_ARG(choice == 0 || choice == 1, "choice must be 0 (automatic) or 1 (one block per row), got %d", choice);
+  ETB_CHECK_ARG(choice >= 0 && choice <= 2, "choice must be 0, 1 or 2, got %d", choice);
   h->kernel_choice = choice;
   return ETB200_OK;
 }
@@ -437,6 +497,7 @@ etb200_error_t etb200_sampler_sample_rows_exchange(
   peers.epoch = epoch;
   peers.rank = my_rank;
   peers.blocks_done = h->d_blocks_done;
+  peers.wait_ns = h->wait_ns;
   if (rows > 0) {
     etb200_error_t err = check_common(h, logits_device, dtype, rows, row_stride_elems, dest_buffers[0]);
     if (err != ETB200_OK) return err;

@@ -26,17 +26,20 @@ namespace etb200 {
 
 constexpr int kCTerms = 32;  // consecutive terms per chunk (one thread's share of a slice)
 #ifndef ETB_MARGIN_PER_TERM
-#define ETB_MARGIN_PER_TERM 2.9802322e-8f  // 2^-25
+#define ETB_MARGIN_PER_TERM 1.4901161e-8f  // 2^-26
 #endif
 constexpr float kMarginPerTerm = ETB_MARGIN_PER_TERM;
 
 // Relative margin around the estimated running sum inside which the true (sequentially
-// rounded) running sum is assumed to lie when `terms` terms have been added: every addition
+// rounded) running sum is assumed to lie when `terms` terms have been added. Every addition
 // is off by at most half a unit of the last place of a sum that only grows, i.e. by at most
 // 2^-24 of the current sum, so terms * 2^-24 bounds the deviation from the exact sum; the
-// constant covers the rounding of the estimate itself (a float prefix sum).
+// margin used is a quarter of that bound (softmax rows stay below a tenth of it: their
+// deviation is mostly the terms that are too small to move the sum at all), plus a constant
+// for the error of the estimate itself (approximate exponentials, a float prefix sum). A row
+// that breaks the assumption is noticed by the walk and left undecided, never mis-summed.
 ETB_HD float binade_margin(long long terms) {
-  return (float)(terms + 64) * kMarginPerTerm + 3.0e-6f;
+  return (float)(terms + 64) * kMarginPerTerm + 2.0e-5f;
 }
 
 constexpr unsigned kEvTail = 1u;  // closes the list of one slice: carries only the prefix behind it
@@ -48,14 +51,14 @@ constexpr unsigned kEvZero = 8u;  // every term of the chunk is zero: it changes
 // non-event chunks of the same slice in front of this chunk (event chunks contribute 0), so
 // the difference of two consecutive events' xbefore is the increment of the run of ordinary
 // chunks between them; that run is summarised in the binade klo of the event in front of it
-// (a chunk whose binade differs from its predecessor's is always an event). `chunk` is the
-// chunk's number inside its slice: the walk asks for its 32 terms by that number when it has
-// to add them one by one.
+// (a chunk whose binade differs from its predecessor's is always an event). `pool` is the slot
+// in which the chunk's 32 terms are staged for the walk (chunks that may have to be added term
+// by term: two open binades, or no summary at all), or -1.
 struct alignas(16) ChunkEvent {
   int a0lo, a1lo, a0hi, a1hi;
   unsigned long long xbefore;
   short klo;
-  short chunk;
+  short pool;
   unsigned short flags;
   unsigned short pad;
 };
@@ -105,19 +108,24 @@ ETB_HD int chunk_increment_fast(const Arr& e, int k, bool* half) {
   return (int)(tot < 33554432.0f ? tot : 33554432.0f);
 }
 
-// The general two-parity summary, term by term in order.
-template <typename Arr>
-ETB_HD SeqSummary chunk_summary_exact(const Arr& e, int k) {
+// The general two-parity summary of a chunk in binade k (27 <= k <= 252), term by term in row
+// order: `at(j)` returns term j. Used for the rare chunk that holds an exact half-way term.
+template <typename At>
+ETB_HD SeqSummary chunk_summary_exact(At at, int k) {
   SeqSummary s;
   seq_identity(&s);
-  for (int j = 0; j < kCTerms; ++j) seq_push(&s, e[j], k);
+  const float inv_u = seq_inv_u(k);
+  for (int j = 0; j < kCTerms; ++j) seq_push_scaled(&s, at(j), inv_u);
   return s;
 }
 
-// Summaries of one chunk for its open binades. Returns the kEvLo / kEvHi flags (0 for a wild
-// chunk); *tie is set when a summary depends on the parity of the significand.
-template <typename Arr>
-ETB_HD unsigned summarise_chunk(const Arr& e, int klo, int khi, SeqSummary* lo, SeqSummary* hi, bool* tie) {
+// Summaries of one chunk for its open binades: `e` holds the terms in any order (the tie-free
+// increments are sums of integers), `at(j)` returns them in row order. Returns the kEvLo /
+// kEvHi flags (0 for a chunk with more than two open binades, which has to be staged and added
+// term by term); *tie is set when a summary depends on the parity of the running significand.
+template <typename Arr, typename At>
+ETB_HD unsigned summarise_chunk(const Arr& e, At at, int klo, int khi, SeqSummary* lo, SeqSummary* hi,
+                                bool* tie) {
   seq_identity(lo);
   seq_identity(hi);
   *tie = false;
@@ -126,26 +134,23 @@ ETB_HD unsigned summarise_chunk(const Arr& e, int klo, int khi, SeqSummary* lo, 
   const int inc = chunk_increment_fast(e, klo, &half);
   lo->a0 = lo->a1 = inc;
   if (half) {
-    *lo = chunk_summary_exact(e, klo);
+    *lo = chunk_summary_exact(at, klo);
     if (lo->a0 != lo->a1) *tie = true;
   }
-  unsigned flags = kEvLo;
-  if (khi != klo) {
-    const int inc_hi = chunk_increment_fast(e, khi, &half);
-    hi->a0 = hi->a1 = inc_hi;
-    if (half) {
-      *hi = chunk_summary_exact(e, khi);
-      if (hi->a0 != hi->a1) *tie = true;
-    }
-    flags |= kEvHi;
+  if (khi == klo) return kEvLo;
+  const int inc_hi = chunk_increment_fast(e, khi, &half);
+  hi->a0 = hi->a1 = inc_hi;
+  if (half) {
+    *hi = chunk_summary_exact(at, khi);
+    if (hi->a0 != hi->a1) *tie = true;
   }
-  return flags;
+  return kEvLo | kEvHi;
 }
 
 // The sequential replay. `events` holds the records of all slices; slice sl owns the
 // n_events[sl] records from first_event[sl] on, in chunk order, the last of them a kEvTail
-// record. `terms(slice, chunk, j)` returns term j of a chunk (called for j = 0..31 in order, only
-// for chunks that must be added term by term). Returns true with the exact sum in *sum, or
+// record. `terms(slot, j)` returns term j of the chunk staged in pool slot `slot` (called for
+// j = 0..31 in order, only for chunks that must be added term by term). Returns true with the exact sum in *sum, or
 // false when some assumption did not hold (nothing is decided then).
 template <typename Terms>
 ETB_HD bool walk_events(const ChunkEvent* events, const int* first_event, const int* n_events,
@@ -190,9 +195,13 @@ ETB_HD bool walk_events(const ChunkEvent* events, const int* first_event, const 
         }
       }
       // the chunk leaves the binade (or was never summarised for it): real float additions
+      if (r.pool < 0) return false;
       float s = seq_value(k, n);
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
       for (int j = 0; j < kCTerms; ++j) {
-        const float t = terms(sl, (int)r.chunk, j);
+        const float t = terms((int)r.pool, j);
 #if defined(__CUDA_ARCH__)
         s = __fadd_rn(s, t);
 #else

@@ -1,32 +1,37 @@
-// Top-p sampling of bf16 rows with one thread-block CLUSTER per row (sm_100a).
+// Top-p sampling of bf16 rows with one thread-block CLUSTER per row (sm_100a), in two kernels.
 // Included by sampler_kernels.cu inside its unnamed namespace (uses its helpers).
 //
 // Why a cluster: a 128 256-entry bf16 row is 250 KB -- it does not fit the shared memory of
 // one SM, and one block walking it tile by tile is bound by the latency of its per-tile
 // rounds. Here the row is cut into slices of up to 16 384 logits, one per block of the
 // cluster (8 blocks for V = 128 256, 16 for V = 256 000); every thread owns ONE chunk of 32
-// consecutive logits, so the whole row is in registers at once and every phase is a single
-// parallel sweep:
+// consecutive logits, so the whole row is on chip at once and every phase is a single
+// parallel sweep.
 //
+// topp_cluster_kernel (one cluster per row, every block does the same):
 //   0. each block pulls its slice into shared memory with one bulk asynchronous copy
 //      (cp.async.bulk, completion on an mbarrier) -- the row's only trip from HBM;
 //   1. row maximum: packed bf16 max per thread, block reduction, exchange of the block maxima
 //      through distributed shared memory (every block writes its value into every block);
-//   2. the table  bit pattern -> e = expf(x / T - max)  is built ONCE per row: each block
-//      evaluates 8192 / cluster_size entries and stores them into all blocks' tables;
-//   3. every thread looks up its 32 terms, sums them (inexactly) and lists the few large
-//      ones in the leader block's candidate list; a block scan plus an exchange of block
-//      totals gives every chunk an estimate of the running sum in front of it;
-//   4. every chunk is turned into integer increments for the binade(s) that estimate allows
-//      (cluster_math.cuh); the few "event" chunks send a 32-byte record to the leader;
-//   5. the leader block (rank 0) replays the exact sequential sum from the records (one warp),
-//      then finishes sample_topp on the candidate list in its shared memory.
+//   2. two things that only need the maximum, side by side: the table  bit pattern ->
+//      e = expf(x / T - max)  is built ONCE per row (each block evaluates 8192 / cluster_size
+//      entries and stores them into all blocks' tables), and every thread sums approximate
+//      exponentials (ex2.approx) of its 32 logits; a block scan plus the exchange of the
+//      block totals -- the same cluster barrier as the table's -- gives every chunk an
+//      estimate of the running sum in front of it;
+//   3. every thread looks up its 32 exact terms, lists the few large ones, and turns the
+//      chunk into integer increments for the binade(s) the estimate allows (cluster_math.cuh);
+//      the few "event" chunks write a 32-byte record (and, where the replay may have to add
+//      them one by one, their 32 terms) to the row's scratch area in global memory.
+// topp_finish_kernel (one small block per row): replays the exact sequential sum from the
+//   records (cluster_math.cuh: walk_events) and finishes sample_topp on the listed candidates.
+//   Splitting it off keeps every block of the first kernel short-lived and alike, and lets
+//   the sequential part of all rows run side by side.
 //
-// The other blocks of the cluster are done after phase 4 and leave. Nothing here waits on a
-// flag: the only waits are hardware cluster barriers and the mbarrier of the bulk copy (whose
-// wait is bounded). A row that this kernel cannot decide (the walk met an assumption that did
-// not hold, or a list overflowed) is appended to `retry_rows` and left untouched; the caller
-// runs those rows through sample_rows_kernel afterwards.
+// Nothing here waits on a flag: the only waits are hardware cluster barriers and the
+// mbarrier of the bulk copy (whose wait is bounded). A row that cannot be decided this way
+// (the replay met an assumption that did not hold, or a list overflowed) is appended to
+// `retry_rows` and left untouched; the caller runs those rows through sample_rows_kernel.
 //
 // No multicast loads are used anywhere: each block copies its own slice.
 
@@ -36,75 +41,54 @@ constexpr int kCThreads = 512;
 constexpr int kCWarps = kCThreads / 32;
 constexpr int kCSliceMax = kCThreads * kCTerms;  // logits per block
 constexpr int kCMaxCluster = 16;
-constexpr int kCEventCap = 512;   // event records per row (all slices together)
-constexpr int kCCandCap = 1024;   // candidate entries per row
+// per slice, in the row's scratch area
+constexpr int kCSliceEvents = 96;   // event records (the last one closes the slice)
+constexpr int kCSliceCand = 192;    // candidate entries
+// per row, in the finishing kernel's shared memory
+constexpr int kFThreads = 256;
+constexpr int kFEventCap = 448;
+constexpr int kFPoolCap = 192;
+constexpr int kFCandCap = 1024;
 
-// The leader's work arrays for the end of sample_topp; they reuse the slice's memory, which
-// is no longer read by then.
-struct ClusterTail {
-  unsigned long long ck[kCCandCap];
-  alignas(16) float p[kCCandCap + 8];
-  int idx[kCCandCap];
-  alignas(16) float prefix[kCCandCap + 4];
+struct SliceHeader {
+  int n_events;  // records written, including the closing one; 0 = the slice gave up
+  int n_cand;
+  int pad0, pad1;
+};
+
+// Scratch of one slice in global memory. The 32 terms of event i (if it is staged) are in
+// terms[i].
+struct SliceScratch {
+  SliceHeader hdr;
+  ChunkEvent events[kCSliceEvents];
+  Entry cand[kCSliceCand];
+  float terms[kCSliceEvents][kCTerms];
 };
 
 struct __align__(128) ClusterShared {
-  union {
-    unsigned short slice[kCSliceMax];  // this block's logits (bf16 bit patterns), row order
-    ClusterTail tail;
-  };
+  unsigned short slice[kCSliceMax];  // this block's logits (bf16 bit patterns), row order
   float lut[kLutSize];               // bit pattern -> e, identical in every block of the cluster
   uint64_t exp_tab[kExpTableSize];
-  unsigned long long mbar;           // completion barrier of the bulk copy
+  unsigned long long mbar;  // completion barrier of the bulk copy
   // written by the peers through distributed shared memory
-  float cmax[kCMaxCluster];          // block maxima
-  double ctot[kCMaxCluster];         // block totals of the estimate
+  float cmax[kCMaxCluster];   // block maxima
+  double ctot[kCMaxCluster];  // block totals of the estimate
   // block-level reductions and scans
   float redf[kCWarps];
   double wtot[kCWarps];
   unsigned long long wx[kCWarps];
   int wev[kCWarps];
   int wklo[kCWarps];
-  int ev_base;
-  // leader only (rank 0); the peers write into the leader's copy
-  int ev_total;
-  int cand_count;
-  int give_up;
-  int ev_first[kCMaxCluster];
-  int ev_count[kCMaxCluster];
-  ChunkEvent events[kCEventCap];
-  Entry cand[kCCandCap];
-  // the leader's tail
-  float sum;
-  float coin;
-  int sum_ok;
-  int n_kept;
-  int last;
-  float cum;
-  int first_above;
+  int lcand_count;
+  Entry lcand[kCSliceCand];  // this slice's candidates, before they go to global memory
 };
-static_assert(sizeof(ClusterTail) <= kCSliceMax * sizeof(unsigned short), "the tail arrays must fit the slice");
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
+// The hardware barrier of the cluster, split so that work can sit between arrival and wait.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
-
-// Bounded wait for the bulk copy (phase 0). Returns false if the copy has not landed after
-// about a second; the row is then handed to the other kernel.
-__device__ __forceinline__ bool wait_bulk_copy(unsigned long long* bar) {
-  const uint32_t a = smem_addr(bar);
-  for (int spin = 0; spin < (1 << 22); ++spin) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(0u)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // e for one bf16 bit pattern: table where covered, direct evaluation otherwise.
@@ -114,66 +98,68 @@ __device__ __forceinline__ float cluster_term(const ClusterShared& sm, uint32_t 
   return expf_ref(__fsub_rn(__fmul_rn(bits_f32(h << 16), inv_t), mx), sm.exp_tab);
 }
 
-// Terms of one chunk for the leader's walk: every lane of the walking warp fetches one term
-// (from the leader's own slice, or from the row in global memory for the other slices) and
-// the terms are handed out by shuffles. All lanes run the walk in lockstep.
-struct LeaderTerms {
-  const ClusterShared* sm;
-  const unsigned short* row;
-  int vocab;
-  int slice_len;
-  float inv_t;
-  float mx;
-  mutable float mine;
-  __device__ __forceinline__ float operator()(int sl, int chunk, int j) const {
-    if (j == 0) {
-      const int lane = threadIdx.x & 31;
-      const int local = chunk * kCTerms + lane;
-      const int i = sl * slice_len + local;
-      uint32_t h = 0xFF80u;  // -inf beyond the row
-      if (sl == 0) {
-        h = sm->slice[local];
-      } else if (i < vocab) {
-        h = __ldg(row + i);
-      }
-      mine = cluster_term(*sm, h, inv_t, mx);
-    }
-    return __shfl_sync(0xffffffffu, mine, j);
+// The eight terms of one 128-bit group of logits.
+__device__ __forceinline__ void cluster_terms8(const ClusterShared& sm, const uint4& raw, float inv_t, float mx,
+                                               float (&e)[8]) {
+  const char* lut_bytes = reinterpret_cast<const char*>(sm.lut);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t bad = 0u;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // both halves of the word at once (see RowMath::eval_raw)
+    const uint32_t wb = w[j] + (kLutBias | (kLutBias << 16));
+    bad |= wb ^ 0x40004000u;
+    const uint32_t off0 = ((wb << 2) & 0x3FFCu) | ((wb >> 1) & 0x4000u);
+    const uint32_t off1 = ((wb >> 14) & 0x3FFCu) | ((wb >> 17) & 0x4000u);
+    e[2 * j] = *reinterpret_cast<const float*>(lut_bytes + off0);
+    e[2 * j + 1] = *reinterpret_cast<const float*>(lut_bytes + off1);
   }
-};
+  if ((bad & 0x70007000u) != 0u) {
+    // rare: a zero, tiny, huge or non-finite logit (or padding) in this group
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      e[2 * j] = cluster_term(sm, w[j] & 0xFFFFu, inv_t, mx);
+      e[2 * j + 1] = cluster_term(sm, w[j] >> 16, inv_t, mx);
+    }
+  }
+}
+
+#if defined(ETB200_PHASE_CLOCKS)
+// Debug build only: clock64 stamps of block 0 / row 0, one per phase boundary.
+__device__ long long g_phase_clock[16];
+#define ETB_STAMP(k)                                                        \
+  do {                                                                      \
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] = clock64();  \
+  } while (0)
+#else
+#define ETB_STAMP(k)
+#endif
 
 __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
-    const unsigned short* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride,
-    int slice_len, float inv_t, float topp, unsigned long long* __restrict__ rng_states,
-    int64_t* __restrict__ out_ids, PeerOut peers, ExpTable table, int* __restrict__ retry_rows,
-    int* __restrict__ retry_count, int* __restrict__ retry_count_next) {
+    const unsigned short* __restrict__ logits, int vocab, int64_t row_stride, int slice_len, float inv_t,
+    float topp, ExpTable table, SliceScratch* __restrict__ scratch) {
   extern __shared__ __align__(128) unsigned char cluster_smem_raw[];
   ClusterShared& sm = *reinterpret_cast<ClusterShared*>(cluster_smem_raw);
   cg::cluster_group cluster = cg::this_cluster();
   const int csize = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t r = (int64_t)(blockIdx.x / csize);
+  const int64_t r = (int64_t)(blockIdx.x / csize);  // row inside this launch
   const unsigned short* row = logits + r * row_stride;
-  ClusterShared* leader = cluster.map_shared_rank(&sm, 0);
+  SliceScratch& out = scratch[r * csize + rank];
 
   const int i0 = rank * slice_len;
   const int len = vocab - i0 < 0 ? 0 : (vocab - i0 < slice_len ? vocab - i0 : slice_len);
   const int n_chunks = (len + kCTerms - 1) / kCTerms;
   const int len16 = len & ~7;  // whole 16-byte units go by the bulk copy
 
+  ETB_STAMP(0);
   // ---- phase 0: the slice comes in; everything that does not need it meanwhile
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&sm.mbar)), "r"(1u));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (rank == 0) {
-      sm.ev_total = 0;
-      sm.cand_count = 0;
-      sm.give_up = 0;
-      // the counter the NEXT launch will use is cleared here (launches of a handle are ordered)
-      if (blockIdx.x == 0) *retry_count_next = 0;
-    }
+    sm.lcand_count = 0;
   }
   // the ragged end of the slice and the padding up to a whole chunk (-inf: e = 0)
   for (int i = len16 + tid; i < n_chunks * kCTerms; i += kCThreads) {
@@ -190,21 +176,21 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
         "l"(row + i0), "r"(bytes), "r"(smem_addr(&sm.mbar))
         : "memory");
   }
-  // the peers' shared memory must exist before anything is stored into it
-  cluster.sync();
+  // barrier 0 ("every block of the cluster is running"): its latency hides behind the copy
+  cluster_arrive();
   bool copy_ok = true;
-  if (len16 > 0) copy_ok = wait_bulk_copy(&sm.mbar);
+  if (len16 > 0) copy_ok = wait_bulk_copy(&sm.mbar, 0u);
 
+  ETB_STAMP(1);
   // ---- phase 1: this thread's chunk (four 128-bit reads, rotated per thread pair so that a
   // warp's reads fall into distinct banks) and the row maximum
   const bool active = tid < n_chunks;
-  const int sw = (tid >> 1) & 3;
+  const int sw = (tid >> 1) & 3;  // register group q holds the chunk's logits (q ^ sw) * 8 ...
   uint4 raw[4];
   float gmax[4];  // maximum of each group of eight logits, for the candidate filter
   {
     const uint4* mine4 = reinterpret_cast<const uint4*>(sm.slice) + tid * 4;
-    const __nv_bfloat162 ninf = neg_inf2(__nv_bfloat16());
-    __nv_bfloat162 acc = ninf;
+    __nv_bfloat162 acc = neg_inf2(__nv_bfloat16());
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       raw[q] = active ? mine4[q ^ sw] : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
@@ -218,6 +204,7 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
     if (lane == 0) sm.redf[warp] = m;
     __syncthreads();
+    cluster_wait();  // barrier 0: the peers' shared memory may be written from here on
     if (tid < csize) {
       float b = sm.redf[0];
 #pragma unroll
@@ -225,7 +212,8 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
       cluster.map_shared_rank(&sm, tid)->cmax[rank] = b;
     }
   }
-  cluster.sync();
+  cluster_arrive();
+  cluster_wait();  // barrier 1: the block maxima are everywhere
   float mx;
   {
     float b = sm.cmax[0];
@@ -233,7 +221,8 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     mx = __fmul_rn(b, inv_t);  // x -> fl(x * inv_t) is monotone for inv_t > 0
   }
 
-  // ---- phase 2: the table, built once per row by the whole cluster
+  ETB_STAMP(2);
+  // ---- phase 2: this block's share of the table (stored into every block), and the estimate
   {
     const int per_block = kLutSize / csize;
     for (int k = tid; k < per_block; k += kCThreads) {
@@ -244,73 +233,23 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
       for (int c = 0; c < csize; ++c) cluster.map_shared_rank(&sm, c)->lut[slot] = e;
     }
   }
-  cluster.sync();
-
-  // ---- phase 3: the 32 terms, their (inexact) sum, the candidates
-  const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
-  const float e_floor = fmaxf(cutoff * 0.999999f, kGuessFloor);
-  float e[kCTerms];
-#pragma unroll
-  for (int j = 0; j < kCTerms; ++j) e[j] = 0.0f;
+  float est = 0.0f;
   if (active) {
-    const char* lut_bytes = reinterpret_cast<const char*>(sm.lut);
-    uint32_t bad = 0u;
+    // sum of 2^((x * inv_t - mx) * log2 e) with the hardware's approximate exponential: good to
+    // about 1e-6, which is all the binade guess needs (binade_margin allows for it)
+    const float c1 = inv_t * 1.4426950408889634f;
+    const float c2 = -mx * 1.4426950408889634f;
+    float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const uint32_t w[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        // both halves of the word at once (see RowMath::eval_raw)
-        const uint32_t wb = w[j] + (kLutBias | (kLutBias << 16));
-        bad |= wb ^ 0x40004000u;
-        const uint32_t off0 = ((wb << 2) & 0x3FFCu) | ((wb >> 1) & 0x4000u);
-        const uint32_t off1 = ((wb >> 14) & 0x3FFCu) | ((wb >> 17) & 0x4000u);
-        e[q * 8 + 2 * j] = *reinterpret_cast<const float*>(lut_bytes + off0);
-        e[q * 8 + 2 * j + 1] = *reinterpret_cast<const float*>(lut_bytes + off1);
+        a4[j] += ex2_approx(fmaf(__uint_as_float(w[j] << 16), c1, c2));
+        a4[j] += ex2_approx(fmaf(__uint_as_float(w[j] & 0xFFFF0000u), c1, c2));
       }
     }
-    if ((bad & 0x70007000u) != 0u) {
-      // rare: a zero, tiny, huge or non-finite logit (or padding) in this chunk
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t w[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          e[q * 8 + 2 * j] = cluster_term(sm, w[j] & 0xFFFFu, inv_t, mx);
-          e[q * 8 + 2 * j + 1] = cluster_term(sm, w[j] >> 16, inv_t, mx);
-        }
-      }
-    }
-  }
-  float est;
-  {
-    float a[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = (e[j] + e[j + 8]) + (e[j + 16] + e[j + 24]);
-    est = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
-  }
-  {
-    // Candidates: e >= e_floor. e is monotone in the logit, so a group of eight can only hold
-    // one if its largest logit reaches a (generously low) bound; the exact test is on e.
-    const float x_bound = (__logf(e_floor) + mx) / inv_t;
-    const float x_low = x_bound - 0.03f * fabsf(x_bound) - 0.0625f;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      if (gmax[q] >= x_low) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (e[q * 8 + j] >= e_floor) {
-            const int slot = atomicAdd(&leader->cand_count, 1);
-            if (slot < kCCandCap) {
-              Entry en;
-              en.key = f32_bits(e[q * 8 + j]);
-              en.idx = i0 + tid * kCTerms + ((q ^ sw) << 3) + j;
-              leader->cand[slot] = en;
-            }
-          }
-        }
-      }
-    }
+    est = (a4[0] + a4[1]) + (a4[2] + a4[3]);
   }
   // block scan of the estimates (float inside a warp, double across warps and blocks)
   float est_incl = est;
@@ -321,70 +260,113 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
   }
   if (lane == 31) sm.wtot[warp] = (double)est_incl;
   __syncthreads();
-  double warp_pre = 0.0, block_tot = 0.0;
+  float p_in, p_out;
+  {
+    double warp_pre = 0.0, block_tot = 0.0;
 #pragma unroll
-  for (int w = 0; w < kCWarps; ++w) {
-    const double t = sm.wtot[w];
-    if (w < warp) warp_pre += t;
-    block_tot += t;
+    for (int w = 0; w < kCWarps; ++w) {
+      const double t = sm.wtot[w];
+      if (w < warp) warp_pre += t;
+      block_tot += t;
+    }
+    if (tid < csize) cluster.map_shared_rank(&sm, tid)->ctot[rank] = block_tot;
+    cluster_arrive();
+    cluster_wait();  // barrier 2: the table and the block totals are everywhere
+    double row_pre = 0.0;
+    for (int c = 0; c < rank; ++c) row_pre += sm.ctot[c];
+    p_out = (float)(row_pre + warp_pre + (double)est_incl);
+    p_in = (float)(row_pre + warp_pre + (double)(est_incl - est));
   }
-  if (tid < csize) cluster.map_shared_rank(&sm, tid)->ctot[rank] = block_tot;
-  cluster.sync();
-  double row_pre = 0.0;
-  for (int c = 0; c < rank; ++c) row_pre += sm.ctot[c];
-  const float p_out = (float)(row_pre + warp_pre + (double)est_incl);
-  const float p_in = (float)(row_pre + warp_pre + (double)(est_incl - est));
 
-  // ---- phase 4: integer increments for the open binade(s); event records to the leader
+  ETB_STAMP(3);
+  // ---- phase 3: the exact terms, eight at a time: candidates and integer increments
+  const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
+  const float e_floor = fmaxf(cutoff * 0.999999f, kGuessFloor);
   int klo = 1, khi = 1;
   SeqSummary slo, shi;
   seq_identity(&slo);
   seq_identity(&shi);
   unsigned flags = 0u;
   bool tie = false;
+  if (active) chunk_binades(p_in, p_out, binade_margin((long long)i0 + (long long)(tid + 1) * kCTerms), &klo, &khi);
+  const bool can_sum = active && chunk_summarisable(klo, khi);
+  const bool two = can_sum && khi != klo;
+  // the second binade is summed by the whole warp whenever one of its chunks needs it
+  const bool warp_two = __any_sync(0xffffffffu, two);
   if (active) {
-    chunk_binades(p_in, p_out, binade_margin((long long)i0 + (long long)(tid + 1) * kCTerms), &klo, &khi);
-    if (est == 0.0f) {
-      flags = kEvLo | kEvHi | kEvZero;  // nothing but zeros: changes no sum
-    } else {
-      if (chunk_summarisable(klo, khi)) {
-        bool half;
-        const int inc = chunk_increment_fast(e, klo, &half);  // a sum of integers: any order
-        slo.a0 = slo.a1 = inc;
-        bool half_hi = false;
-        if (khi != klo) {
-          const int inc_hi = chunk_increment_fast(e, khi, &half_hi);
-          shi.a0 = shi.a1 = inc_hi;
-          flags = kEvLo | kEvHi;
-        } else {
-          flags = kEvLo;
-        }
-        if (half || half_hi) {
-          // rare: an exact half-way term; the two-parity summary needs the terms in row order
-          float ord[kCTerms];
+    // Candidates: e >= e_floor. e is monotone in the logit, so a group of eight can only hold
+    // one if its largest logit reaches a (generously low) bound; the exact test is on e.
+    const float x_bound = (__logf(e_floor) + mx) / inv_t;
+    const float x_low = x_bound - 0.03f * fabsf(x_bound) - 0.0625f;
+    const float inv_lo = seq_inv_u(can_sum ? klo : 127), inv_hi = seq_inv_u(can_sum ? khi : 127);
+    float acc_lo[2] = {0.0f, 0.0f}, acc_hi[2] = {0.0f, 0.0f};
+    float md_lo = 0.0f, md_hi = 0.0f;
 #pragma unroll
-          for (int j = 0; j < kCTerms; ++j) ord[(((j >> 3) ^ sw) << 3) | (j & 7)] = e[j];
-          if (half) {
-            slo = chunk_summary_exact(ord, klo);
-            tie = tie || slo.a0 != slo.a1;
+    for (int q = 0; q < 4; ++q) {
+      float e[8];
+      cluster_terms8(sm, raw[q], inv_t, mx, e);
+      if (gmax[q] >= x_low) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (e[j] >= e_floor) {
+            const int slot = atomicAdd(&sm.lcand_count, 1);
+            if (slot < kCSliceCand) {
+              Entry en;
+              en.key = f32_bits(e[j]);
+              en.idx = i0 + tid * kCTerms + ((q ^ sw) << 3) + j;
+              sm.lcand[slot] = en;
+            }
           }
-          if (half_hi) {
-            shi = chunk_summary_exact(ord, khi);
-            tie = tie || shi.a0 != shi.a1;
-          }
+        }
+      }
+      inc8(e, inv_lo, acc_lo, md_lo);  // sums of integers: the order does not matter
+      if (warp_two) inc8(e, inv_hi, acc_hi, md_hi);
+    }
+    // a chunk whose largest logit already gives e = 0 holds nothing but zeros
+    const float top = fmaxf(fmaxf(gmax[0], gmax[1]), fmaxf(gmax[2], gmax[3]));
+    if (__fsub_rn(__fmul_rn(top, inv_t), mx) < -0x1.9fe368p6f) {
+      flags = kEvLo | kEvHi | kEvZero;
+    } else if (can_sum) {
+      const float tlo = acc_lo[0] + acc_lo[1], thi = acc_hi[0] + acc_hi[1];
+      slo.a0 = slo.a1 = (int)(tlo < 33554432.0f ? tlo : 33554432.0f);
+      flags = kEvLo;
+      bool half_lo = !(md_lo < 0.5f), half_hi = false;
+      if (two) {
+        shi.a0 = shi.a1 = (int)(thi < 33554432.0f ? thi : 33554432.0f);
+        half_hi = !(md_hi < 0.5f);
+        flags = kEvLo | kEvHi;
+      }
+      if (half_lo || half_hi) {
+        // rare: an exact half-way term; the two-parity summary needs the terms in row order
+        float ord[kCTerms];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float e[8];
+          cluster_terms8(sm, raw[q], inv_t, mx, e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ord[((q ^ sw) << 3) + j] = e[j];
+        }
+        const float* po = ord;
+        if (half_lo) {
+          slo = chunk_summary_exact([po](int j) { return po[j]; }, klo);
+          tie = tie || slo.a0 != slo.a1;
+        }
+        if (half_hi) {
+          shi = chunk_summary_exact([po](int j) { return po[j]; }, khi);
+          tie = tie || shi.a0 != shi.a1;
         }
       }
     }
   }
+  ETB_STAMP(4);
   const bool zero = (flags & kEvZero) != 0u;
-  const bool wild = active && flags == 0u;
-  const bool unsafe = active && !zero && (flags & kEvHi) != 0u;
+  const bool staged = active && !zero && flags != kEvLo;  // two open binades, or no summary
   // a chunk whose binade differs from its predecessor's is an event; so is the first of a slice
   int prev_klo = __shfl_up_sync(0xffffffffu, klo, 1);
   if (lane == 31) sm.wklo[warp] = klo;
-  __syncthreads();
+  __syncthreads();  // also: every candidate of this slice is in sm.lcand
   if (lane == 0) prev_klo = warp > 0 ? sm.wklo[warp - 1] : -1;
-  const bool event = active && (tid == 0 || klo != prev_klo || wild || unsafe || tie);
+  const bool event = active && (tid == 0 || klo != prev_klo || staged || tie);
   // exclusive scans over the block: increments of the ordinary chunks, and event slots
   const unsigned inc_mine = (active && !event) ? (unsigned)slo.a0 : 0u;  // < 2^24 for a valid run
   unsigned inc_incl = inc_mine;
@@ -412,19 +394,28 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     x_tot += xv;
     ev_tot += c;
   }
+  const int n_lc = sm.lcand_count;
+  const bool fits = ev_tot + 1 <= kCSliceEvents && n_lc <= kCSliceCand && copy_ok;
   if (tid == 0) {
-    // one slot range per slice in the leader's list (plus the record that closes the slice)
-    const int base = atomicAdd(&leader->ev_total, ev_tot + 1);
-    const bool fits = base + ev_tot + 1 <= kCEventCap;
-    leader->ev_first[rank] = fits ? base : 0;
-    leader->ev_count[rank] = fits ? ev_tot + 1 : 0;
-    if (!fits || !copy_ok) leader->give_up = 1;
-    sm.ev_base = fits ? base : -1;
+    SliceHeader h;
+    h.n_events = fits ? ev_tot + 1 : 0;
+    h.n_cand = fits ? n_lc : 0;
+    h.pad0 = h.pad1 = 0;
+    out.hdr = h;
   }
-  __syncthreads();
-  const int ev_base = sm.ev_base;
-  if (ev_base >= 0) {
+  if (fits) {
     if (event) {
+      const int slot = ev_pre + __popc(evb & ((1u << lane) - 1u));
+      if (staged) {
+        float4* dst = reinterpret_cast<float4*>(out.terms[slot]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float e[8];
+          cluster_terms8(sm, raw[q], inv_t, mx, e);
+          dst[(q ^ sw) * 2] = make_float4(e[0], e[1], e[2], e[3]);
+          dst[(q ^ sw) * 2 + 1] = make_float4(e[4], e[5], e[6], e[7]);
+        }
+      }
       ChunkEvent rec;
       rec.a0lo = slo.a0;
       rec.a1lo = slo.a1;
@@ -432,69 +423,190 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
       rec.a1hi = shi.a1;
       rec.xbefore = x_pre + (unsigned long long)(inc_incl - inc_mine);
       rec.klo = (short)klo;
-      rec.chunk = (short)tid;
+      rec.pool = (short)(staged ? slot : -1);
       rec.flags = (unsigned short)flags;
       rec.pad = 0;
-      leader->events[ev_base + ev_pre + __popc(evb & ((1u << lane) - 1u))] = rec;
+      out.events[slot] = rec;
     }
     if (tid == 0) {
       ChunkEvent rec;
       rec.a0lo = rec.a1lo = rec.a0hi = rec.a1hi = 0;
       rec.xbefore = x_tot;
       rec.klo = 0;
-      rec.chunk = 0;
+      rec.pool = -1;
       rec.flags = (unsigned short)kEvTail;
       rec.pad = 0;
-      leader->events[ev_base + ev_tot] = rec;
+      out.events[ev_tot] = rec;
     }
+    for (int i = tid; i < n_lc; i += kCThreads) out.cand[i] = sm.lcand[i];
   }
-  cluster.sync();
-  if (rank != 0) return;
+  ETB_STAMP(5);
+}
 
-  // ---- phase 5 (leader): the exact sequential sum, replayed by one warp
-  if (warp == 0) {
-    LeaderTerms terms;
-    terms.sm = &sm;
-    terms.row = row;
-    terms.vocab = vocab;
-    terms.slice_len = slice_len;
-    terms.inv_t = inv_t;
-    terms.mx = mx;
-    terms.mine = 0.0f;
-    float s = 0.0f;
-    bool ok = sm.give_up == 0 && sm.cand_count <= kCCandCap;
-    if (ok) ok = walk_events(sm.events, sm.ev_first, sm.ev_count, csize, kCEventCap, terms, &s);
-    if (lane == 0) {
-      sm.sum = s;
-      sm.sum_ok = ok ? 1 : 0;
-      sm.n_kept = 0;
-      sm.first_above = 0x7fffffff;
-      unsigned long long st = rng_states[r];
-      sm.coin = next_coin(&st);  // the state is stored only when the row is decided
+// ---------------------------------------------------------------------------------------
+// One block per row: gathers the row's records, replays the exact sum, finishes sample_topp.
+// ---------------------------------------------------------------------------------------
+struct FinishTail {
+  unsigned long long ck[kFCandCap];
+  alignas(16) float p[kFCandCap + 8];
+  int idx[kFCandCap];
+  alignas(16) float prefix[kFCandCap + 4];
+};
+
+struct __align__(16) FinishShared {
+  union {
+    struct {
+      ChunkEvent events[kFEventCap];
+      float pool[kFPoolCap][kCTerms];
+    } w;              // the replay
+    FinishTail tail;  // after it
+  };
+  Entry cand[kFCandCap];
+  int ev_first[kCMaxCluster];
+  int ev_count[kCMaxCluster];
+  int cand_first[kCMaxCluster];
+  int cand_count[kCMaxCluster];
+  int warp_staged[kFThreads / 32];
+  int ok;
+  int n_staged;
+  float sum;
+  float coin;
+  int n_kept;
+  int last;
+  float cum;
+  int first_above;
+};
+
+__global__ void __launch_bounds__(kFThreads) topp_finish_kernel(
+    const SliceScratch* __restrict__ scratch, int64_t row0, int64_t rows, int vocab, int csize, float topp,
+    unsigned long long* __restrict__ rng_states, int64_t* __restrict__ out_ids, PeerOut peers,
+    int* __restrict__ retry_rows, int* __restrict__ retry_count, int* __restrict__ retry_count_next) {
+  extern __shared__ __align__(16) unsigned char finish_smem_raw[];
+  FinishShared& sm = *reinterpret_cast<FinishShared*>(finish_smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t rl = blockIdx.x;    // row inside this launch
+  const int64_t r = row0 + rl;      // row of the batch
+  const SliceScratch* sl0 = scratch + rl * csize;
+  ETB_STAMP(6);
+  // the counter the NEXT call will use is cleared here (calls of a handle are ordered)
+  if (blockIdx.x == 0 && tid == 0 && retry_count_next != nullptr) *retry_count_next = 0;
+
+  // ---- the slices' headers, and where each slice's records go
+  if (tid == 0) {
+    int e = 0, c = 0;
+    bool ok = true;
+    for (int s = 0; s < csize; ++s) {
+      const SliceHeader h = sl0[s].hdr;
+      if (h.n_events < 1 || h.n_events > kCSliceEvents || h.n_cand < 0 || h.n_cand > kCSliceCand) ok = false;
+      sm.ev_first[s] = e;
+      sm.ev_count[s] = ok ? h.n_events : 0;
+      sm.cand_first[s] = c;
+      sm.cand_count[s] = ok ? h.n_cand : 0;
+      if (ok) {
+        e += h.n_events;
+        c += h.n_cand;
+      }
     }
+    if (e > kFEventCap || c > kFCandCap) ok = false;
+    sm.ok = ok ? 1 : 0;
+    sm.n_kept = 0;
+    sm.first_above = 0x7fffffff;
+    sm.n_staged = 0;
+    unsigned long long st = rng_states[r];
+    sm.coin = next_coin(&st);  // the state is stored only when the row is decided
   }
   __syncthreads();
-  bool decided = sm.sum_ok != 0;
+  bool decided = sm.ok != 0;
+  int n_c = 0;
+  if (decided) {
+    // ---- records, candidates and the staged terms into shared memory
+    for (int s = 0; s < csize; ++s) {
+      const int ne = sm.ev_count[s], e0 = sm.ev_first[s];
+      const uint4* src = reinterpret_cast<const uint4*>(sl0[s].events);
+      uint4* dst = reinterpret_cast<uint4*>(sm.w.events + e0);
+      for (int i = tid; i < ne * 2; i += kFThreads) dst[i] = __ldg(src + i);
+      const int nc = sm.cand_count[s], c0 = sm.cand_first[s];
+      for (int i = tid; i < nc; i += kFThreads) sm.cand[c0 + i] = sl0[s].cand[i];
+    }
+    n_c = sm.cand_first[csize - 1] + sm.cand_count[csize - 1];
+    __syncthreads();
+    // staged chunks get consecutive pool slots, in event order
+    const int n_ev = sm.ev_first[csize - 1] + sm.ev_count[csize - 1];
+    int pre = 0;
+    for (int base = 0; base < n_ev; base += kFThreads) {
+      const int i = base + tid;
+      const bool st = i < n_ev && sm.w.events[i].pool >= 0;
+      const unsigned b = __ballot_sync(0xffffffffu, st);
+      if (lane == 0) sm.warp_staged[warp] = __popc(b);
+      __syncthreads();
+      int mine = pre;
+      for (int w = 0; w < kFThreads / 32; ++w) {
+        if (w < warp) mine += sm.warp_staged[w];
+        pre += sm.warp_staged[w];
+      }
+      if (st) {
+        const int slot = mine + __popc(b & ((1u << lane) - 1u));
+        // which slice this record came from
+        int s = 0;
+        while (s + 1 < csize && i >= sm.ev_first[s + 1]) ++s;
+        const int local = i - sm.ev_first[s];
+        if (slot < kFPoolCap) {
+          const float4* src = reinterpret_cast<const float4*>(sl0[s].terms[local]);
+          float4* dst = reinterpret_cast<float4*>(sm.w.pool[slot]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) dst[k] = __ldg(src + k);
+          sm.w.events[i].pool = (short)slot;
+        } else {
+          sm.w.events[i].pool = -1;  // no room: the replay gives up if it needs these terms
+        }
+      }
+      __syncthreads();
+    }
+    ETB_STAMP(7);
+    // ---- the exact sequential sum, replayed by one thread
+    if (tid == 0) {
+      float s = 0.0f;
+      const float(*pool)[kCTerms] = sm.w.pool;
+      const bool ok = walk_events(sm.w.events, sm.ev_first, sm.ev_count, csize, kFEventCap,
+                                  [pool](int slot, int j) { return pool[slot][j]; }, &s);
+      sm.sum = s;
+      sm.ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    decided = sm.ok != 0;
+  }
+  ETB_STAMP(8);
   const float sum = sm.sum;
   const float coin = sm.coin;
+  const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
+  const float e_floor = fmaxf(cutoff * 0.999999f, kGuessFloor);
 
-  // ---- phase 6 (leader): sample_topp (sampler.cpp:122-171) on the candidate list
+  // ---- sample_topp (sampler.cpp:122-171) on the candidate list
   int token = 0;
   if (decided) {
-    const int n_c = sm.cand_count;
     // crop (sampler.cpp:136-143) and sort key: probability descending, index ascending
-    for (int i = tid; i < n_c; i += kCThreads) {
-      const Entry en = sm.cand[i];
-      const float p = __fdiv_rn(bits_f32(en.key), sum);
-      if (p >= cutoff) {
-        const int slot = atomicAdd(&sm.n_kept, 1);
-        sm.tail.ck[slot] = ((unsigned long long)f32_bits(p) << 32) | (uint32_t)(0x7FFFFFFF - en.idx);
+    for (int ib = 0; ib < n_c; ib += kFThreads) {
+      const int i = ib + tid;
+      bool keep = false;
+      unsigned long long ck = 0ull;
+      if (i < n_c) {
+        const Entry en = sm.cand[i];
+        const float p = __fdiv_rn(bits_f32(en.key), sum);
+        keep = p >= cutoff;
+        ck = ((unsigned long long)f32_bits(p) << 32) | (uint32_t)(0x7FFFFFFF - en.idx);
+      }
+      const unsigned bal = __ballot_sync(0xffffffffu, keep);
+      if (bal != 0u) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&sm.n_kept, __popc(bal));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (keep) sm.tail.ck[base + __popc(bal & ((1u << lane) - 1u))] = ck;
       }
     }
     __syncthreads();
     const int n_b = sm.n_kept;
     if (n_b > 0) {
-      for (int i = tid; i < n_b; i += kCThreads) {
+      for (int i = tid; i < n_b; i += kFThreads) {
         const unsigned long long mine = sm.tail.ck[i];
         int rank_i = 0;
 #pragma unroll 8
@@ -548,7 +660,7 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
       decided = false;
     } else {
       const float rr = __fmul_rn(coin, sm.cum);  // sampler.cpp:162
-      for (int i0b = 0; i0b <= last; i0b += kCThreads) {
+      for (int i0b = 0; i0b <= last; i0b += kFThreads) {
         const int i = i0b + tid;
         const bool above = i <= last && sm.tail.prefix[i] > rr;
         const unsigned bal = __ballot_sync(0xffffffffu, above);
@@ -559,6 +671,7 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
       token = sm.tail.idx[fa <= last ? fa : last];
     }
   }
+  ETB_STAMP(9);
   if (decided) {
     store_token(out_ids, peers, r, token);
     if (tid == 0) {

@@ -74,10 +74,36 @@ struct Entry {
   int32_t idx;   // token index
 };
 
-template <bool kLut>
+// Shared state of the estimate-guided sum (guided_sum.cuh), present only in the kernel
+// variant that uses it.
+constexpr int kGTile = kThreads * kCTerms;  // logits per tile: one chunk of 32 per thread
+constexpr int kGMaxTiles = 16;
+constexpr int kGEventCap = 256;
+constexpr int kGPoolCap = 80;
+
+struct GuidedShared {
+  unsigned long long mbar;  // completion barrier of the tile copies; phases alternate
+  int ok;
+  float sum;
+  int ev_first[1];
+  int ev_count[1];
+  double wtot[2][kWarps];
+  unsigned long long wx[2][kWarps];
+  int wev[2][kWarps];
+  int wst[2][kWarps];
+  int wcand[2][kWarps];
+  int wklo[2][kWarps];
+  ChunkEvent events[kGEventCap];
+  float pool[kGPoolCap][kCTerms];
+  unsigned short kb[kGMaxTiles][kThreads];  // per chunk: lower open binade | (open binades - 1) << 8
+};
+struct NoGuidedShared {};
+
+template <bool kLut, bool kGuided = false>
 struct __align__(16) Shared {
   // (members read with vector loads carry their own alignas)
   static constexpr bool kHasLut = kLut;
+  typename std::conditional<kGuided, GuidedShared, NoGuidedShared>::type g;
   uint64_t exp_tab[kExpTableSize];
   float lut[kLut ? kLutSize : 2];
   alignas(16) float head[kHead];  // read as float4
@@ -623,9 +649,14 @@ __device__ __forceinline__ void store_token(
 
 // Arrival barrier among the GPUs of a node at the end of a launch (see PeerOut). Every thread
 // of every block calls it once, after its last store_token. No kernel of one GPU waits for
-// another kernel of the same GPU; the wait for the other GPUs is limited (about a second),
-// after which the launch records kStatusPeerTimeout in *status and ends.
-constexpr unsigned kArriveSpinLimit = 1u << 21;
+// another kernel of the same GPU; the wait for the other GPUs is limited to peers.wait_ns
+// nanoseconds of the GPU's global timer, after which the launch records kStatusPeerTimeout in
+// *status and ends (the context stays usable; the ids of the missing ranks are stale).
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void peer_arrival_barrier(const PeerOut& peers, int* status) {
   if (peers.epoch == 0ull) return;  // launch-uniform
@@ -644,9 +675,11 @@ __device__ __forceinline__ void peer_arrival_barrier(const PeerOut& peers, int* 
     volatile unsigned long long* theirs = peers.arrive[threadIdx.x] + peers.rank;
     *theirs = peers.epoch;  // tell rank threadIdx.x that this rank's ids are in its buffer
     volatile unsigned long long* mine = peers.arrive[peers.rank] + threadIdx.x;
+    const unsigned long long t0 = global_timer_ns();
     unsigned spins = 0;
     while (*mine < peers.epoch) {  // until rank threadIdx.x has told this rank
-      if (++spins > kArriveSpinLimit) {
+      // the timer is read every 64 polls; the poll count is a second, independent bound
+      if ((++spins & 63u) == 0u && (global_timer_ns() - t0 > peers.wait_ns || spins > (1u << 30))) {
         atomicExch(status, kStatusPeerTimeout);
         break;
       }
@@ -1341,17 +1374,20 @@ __device__ bool small_tail(
   return true;
 }
 
+#include "guided_sum.cuh"
+
 // ---------------------------------------------------------------------------------------
 // The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
 // otherwise. Follows Sampler::sample<float> (sampler.cpp:222-251).
 // ---------------------------------------------------------------------------------------
-template <typename T, bool kLut>
+template <typename T, bool kLut, bool kGuided>
 __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
     float topp, int topk, unsigned long long* __restrict__ rng_states,
     int64_t* __restrict__ out_ids, PeerOut peers, Entry* scratch, ExpTable table,
-    int* __restrict__ status, const int* __restrict__ row_list, const int* __restrict__ row_count) {
-  using S = Shared<kLut>;
+    int* __restrict__ status, const int* __restrict__ row_list, const int* __restrict__ row_count,
+    int* __restrict__ retry_rows, int* __restrict__ retry_count, int* __restrict__ retry_count_next) {
+  using S = Shared<kLut, kGuided>;
   // the block's shared state exceeds the 48 KB static limit: dynamic shared memory, sized
   // sizeof(S) by the launcher
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -1363,6 +1399,15 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   // only e >= guess; if that turns out to be too high for a row, the row is regathered with
   // its exact floor and the guess is lowered for the block's later rows.
   float guess = kGuessFloor;
+  uint32_t copy_parity = 0u;  // phase of the tile-copy barrier (guided variant)
+  if constexpr (kGuided) {
+    if (tid == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&sm.g.mbar)), "r"(1u));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      // the retry counter that the NEXT call will use is cleared here (calls are ordered)
+      if (blockIdx.x == 0 && retry_count_next != nullptr) *retry_count_next = 0;
+    }
+  }
   __syncthreads();
   // mode selection of Sampler::sample (sampler.cpp:239-248): top-k wins over top-p
   const bool use_topk = topk > 0 && topk < vocab;
@@ -1386,11 +1431,13 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     // ---- pass 1: max of the scaled logits
     rm.mx = row_max_scaled<T>(sm, rm.row, vocab, rm.vec_ok, inv_t);
 
-    // the coin is drawn once per sampled row (sampler.cpp:237)
+    // the coin is drawn once per sampled row (sampler.cpp:237); the guided variant stores the
+    // advanced state only once it knows that it decides the row
+    unsigned long long st_next = 0ull;
     if (tid == 0) {
-      unsigned long long st = rng_states[r];
-      sm.misc_f[0] = next_coin(&st);
-      rng_states[r] = st;
+      st_next = rng_states[r];
+      sm.misc_f[0] = next_coin(&st_next);
+      if constexpr (!kGuided) rng_states[r] = st_next;
     }
     if constexpr (kLut) {
       rm.build_lut(sm);  // the previous row's readers are behind the barriers of block_max
@@ -1407,6 +1454,24 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     const float e_floor = use_list ? fmaxf(exact_floor0, guess) : 0.0f;
     float s = 0.0f;
     int n_a = 0;
+    if constexpr (kGuided) {
+      // estimate-guided sum (guided_sum.cuh); a row it does not take or cannot decide goes to the
+      // retry list, untouched, for the variant without it
+      __syncthreads();  // the table is complete
+      bool ok = false;
+      if constexpr (sizeof(T) == 2) {
+        if (rm.vec_ok && vocab <= kGMaxTiles * kGTile) {
+          ok = guided_sum_pass(sm, rm, copy_parity, use_list, e_floor, listA, &n_a, &s);
+        }
+      }
+      if (!ok) {
+        if (tid == 0) retry_rows[atomicAdd(retry_count, 1)] = (int)r;
+        __syncthreads();
+        continue;
+      }
+      if (tid == 0) rng_states[r] = st_next;
+    }
+    if constexpr (!kGuided) {
     {
       // head: the first kHead terms are added by one thread (a sum changes binade every few
       // additions at its start); their candidates are listed by all threads meanwhile
@@ -1535,6 +1600,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       }
       if (first_tile) sum_staged_tile<false>(sm, s, 0.0f, vocab, &hp, &hs);
     }
+    }  // !kGuided
     const float sum = s;
     __syncthreads();
     const float coin = sm.misc_f[0];
@@ -1816,10 +1882,10 @@ int sampler_threads() { return kThreads; }
 
 // Opts the kernel in to its dynamic shared-memory size (once per device would do; the call is
 // cheap and idempotent).
-template <typename T, bool kLut>
+template <typename T, bool kLut, bool kGuided = false>
 static cudaError_t prepare_sample_kernel() {
-  return cudaFuncSetAttribute(sample_rows_kernel<T, kLut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)sizeof(Shared<kLut>));
+  return cudaFuncSetAttribute(sample_rows_kernel<T, kLut, kGuided>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)sizeof(Shared<kLut, kGuided>));
 }
 
 template <typename T, bool kLut>
@@ -1830,10 +1896,25 @@ static cudaError_t launch_sample_t(
     cudaStream_t stream) {
   const cudaError_t attr = prepare_sample_kernel<T, kLut>();
   if (attr != cudaSuccess) return attr;
-  sample_rows_kernel<T, kLut><<<blocks, kThreads, sizeof(Shared<kLut>), stream>>>(
+  sample_rows_kernel<T, kLut, false><<<blocks, kThreads, sizeof(Shared<kLut>), stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       peers,
-      static_cast<Entry*>(scratch), table, status, row_list, row_count);
+      static_cast<Entry*>(scratch), table, status, row_list, row_count, nullptr, nullptr, nullptr);
+  return cudaGetLastError();
+}
+
+template <typename T, bool kLut>
+static cudaError_t launch_guided_t(
+    const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
+    int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, void* scratch,
+    int blocks, const ExpTable& table, int* status, int* retry_rows, int* retry_count,
+    int* retry_count_next, cudaStream_t stream) {
+  const cudaError_t attr = prepare_sample_kernel<T, kLut, true>();
+  if (attr != cudaSuccess) return attr;
+  sample_rows_kernel<T, kLut, true><<<blocks, kThreads, sizeof(Shared<kLut, true>), stream>>>(
+      static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
+      peers, static_cast<Entry*>(scratch), table, status, nullptr, nullptr, retry_rows, retry_count,
+      retry_count_next);
   return cudaGetLastError();
 }
 
@@ -1860,48 +1941,116 @@ cudaError_t launch_sample_rows(
   }
 }
 
+bool guided_supported(int dtype) { return dtype == kDtypeBFloat16 || dtype == kDtypeHalf; }
+
+cudaError_t launch_sample_rows_guided(
+    int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
+    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers,
+    void* scratch, int blocks, const ExpTable& table, int* status, int* retry_rows, int* retry_count,
+    int* retry_count_next, cudaStream_t stream) {
+  switch (dtype) {
+    case kDtypeHalf:
+      return launch_guided_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp, topk, rng_states,
+                                            out_ids, peers, scratch, blocks, table, status, retry_rows,
+                                            retry_count, retry_count_next, stream);
+    case kDtypeBFloat16:
+      return launch_guided_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp, topk,
+                                                  rng_states, out_ids, peers, scratch, blocks, table, status,
+                                                  retry_rows, retry_count, retry_count_next, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
+int guided_kernel_max_blocks_per_sm(int dtype) {
+  int n = 0;
+  cudaError_t e;
+  if (dtype == kDtypeHalf) {
+    e = prepare_sample_kernel<__half, false, true>();
+    if (e == cudaSuccess)
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half, false, true>, kThreads,
+                                                        sizeof(Shared<false, true>));
+  } else {
+    e = prepare_sample_kernel<__nv_bfloat16, true, true>();
+    if (e == cudaSuccess)
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16, true, true>,
+                                                        kThreads, sizeof(Shared<true, true>));
+  }
+  if (e != cudaSuccess || n < 1) n = 1;
+  return n;
+}
+
 bool topp_cluster_supported(int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride,
                             float inv_t, float topp, int topk) {
   if (dtype != kDtypeBFloat16 || !(inv_t > 0.0f) || topk > 0) return false;
   if (!(topp > 0.0f && topp < 1.0f)) return false;
   if (vocab < kClusterMinVocab || vocab > kCMaxCluster * kCSliceMax) return false;
-  if (rows < 1 || rows > (int64_t)0x7fffffff / kCMaxCluster) return false;
+  if (rows < 1 || rows > (int64_t)0x7fffffff) return false;
   // every row must start on a 16-byte boundary (bulk copies)
   if ((reinterpret_cast<uintptr_t>(logits) & 15u) != 0) return false;
   if (rows > 1 && ((row_stride * 2) & 15) != 0) return false;
   return true;
 }
 
+static int cluster_size_for(int vocab) {
+  int csize = 1;
+  while (csize * kCSliceMax < vocab) csize *= 2;
+  return csize;
+}
+
+size_t topp_cluster_scratch_bytes(int vocab, int64_t batch_rows) {
+  return (size_t)batch_rows * (size_t)cluster_size_for(vocab) * sizeof(SliceScratch);
+}
+
 cudaError_t launch_topp_cluster(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
     unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, const ExpTable& table,
-    int* retry_rows, int* retry_count, int* retry_count_next, cudaStream_t stream) {
-  int csize = 1;
-  while (csize * kCSliceMax < vocab) csize *= 2;
+    void* scratch, int64_t batch_rows, int* retry_rows, int* retry_count, int* retry_count_next,
+    cudaStream_t stream) {
+  const int csize = cluster_size_for(vocab);
   const int slice_len = ((vocab + csize * kCTerms - 1) / (csize * kCTerms)) * kCTerms;
   cudaError_t e = cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)sizeof(ClusterShared));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(topp_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)sizeof(FinishShared));
   if (e != cudaSuccess) return e;
   if (csize > 8) {
     e = cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return e;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(rows * csize), 1, 1);
-  cfg.blockDim = dim3(kCThreads, 1, 1);
-  cfg.dynamicSmemBytes = sizeof(ClusterShared);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)csize;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, topp_cluster_kernel, static_cast<const unsigned short*>(logits), rows,
-                            vocab, row_stride, slice_len, inv_t, topp, rng_states, out_ids, peers, table,
-                            retry_rows, retry_count, retry_count_next);
+  const unsigned short* base = static_cast<const unsigned short*>(logits);
+  for (int64_t row0 = 0; row0 < rows; row0 += batch_rows) {
+    const int64_t n = rows - row0 < batch_rows ? rows - row0 : batch_rows;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n * csize), 1, 1);
+    cfg.blockDim = dim3(kCThreads, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(ClusterShared);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, topp_cluster_kernel, base + row0 * row_stride, vocab, row_stride, slice_len,
+                           inv_t, topp, table, static_cast<SliceScratch*>(scratch));
+    if (e != cudaSuccess) return e;
+    topp_finish_kernel<<<(unsigned)n, kFThreads, sizeof(FinishShared), stream>>>(
+        static_cast<const SliceScratch*>(scratch), row0, rows, vocab, csize, topp, rng_states, out_ids, peers,
+        retry_rows, retry_count, row0 == 0 ? retry_count_next : nullptr);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
+
+#if defined(ETB200_PHASE_CLOCKS)
+extern "C" __attribute__((visibility("default"))) int etb200_debug_phase_clocks(long long* out16) {
+  return (int)cudaMemcpyFromSymbol(out16, g_phase_clock, sizeof(long long) * 16);
+}
+#endif
 
 cudaError_t launch_argmax_rows(
     int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, int64_t* out_ids,
@@ -1936,19 +2085,19 @@ int sample_kernel_max_blocks_per_sm(int dtype) {
     case kDtypeFloat:
       e = prepare_sample_kernel<float, false>();
       if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float, false>, kThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<float, false, false>, kThreads,
                                                           sizeof(Shared<false>));
       break;
     case kDtypeHalf:
       e = prepare_sample_kernel<__half, false>();
       if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half, false>, kThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__half, false, false>, kThreads,
                                                           sizeof(Shared<false>));
       break;
     default:
       e = prepare_sample_kernel<__nv_bfloat16, true>();
       if (e == cudaSuccess)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16, true>,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sample_rows_kernel<__nv_bfloat16, true, false>,
                                                           kThreads, sizeof(Shared<true>));
       break;
   }

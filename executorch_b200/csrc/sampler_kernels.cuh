@@ -27,13 +27,14 @@ struct PeerOut {
   long long offset;
   // Optional arrival barrier at the end of the launch (epoch != 0): arrive[p] is rank p's
   // array of kMaxPeers 64-bit arrival marks. When the last block of this launch is done it
-  // writes `epoch` into arrive[p][rank] of every rank p and then waits, with a limit, until
+  // writes `epoch` into arrive[p][rank] of every rank p and then waits, at most wait_ns, until
   // arrive[rank][q] >= epoch for every q: when the launch completes, this GPU's buffer holds
   // the ids of all ranks. blocks_done is a counter of this GPU that is zero between launches.
   unsigned long long* arrive[kMaxPeers];
   unsigned long long epoch;
   int rank;
   int* blocks_done;
+  unsigned long long wait_ns;  // limit of that wait, in nanoseconds of the GPU's global timer
 };
 
 // Bytes of candidate-list scratch the sampling kernel needs when launched with `blocks`
@@ -55,18 +56,34 @@ cudaError_t launch_sample_rows(
     void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream,
     const int* row_list = nullptr, const int* row_count = nullptr);
 
-// Top-p sampling of bf16 rows with one thread-block cluster per row (the fast path). Rows it
-// cannot decide are appended to retry_rows (their count in *retry_count) with their rng state
-// and output untouched; the caller then runs launch_sample_rows with that list on the same
-// stream. *retry_count must be zero when the kernel starts; the kernel clears
-// *retry_count_next for the launch after it.
+// launch_sample_rows for 16-bit logits with the estimate-guided exact sum (the default path):
+// every row is sampled unless the kernel cannot decide it, in which case the row -- rng state
+// and output untouched -- is appended to retry_rows (count in *retry_count, which must be zero
+// at launch) and the caller runs launch_sample_rows with that list on the same stream.
+bool guided_supported(int dtype);
+int guided_kernel_max_blocks_per_sm(int dtype);
+cudaError_t launch_sample_rows_guided(
+    int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
+    float topp, int topk, unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers,
+    void* scratch, int blocks, const ExpTable& table, int* status, int* retry_rows, int* retry_count,
+    int* retry_count_next, cudaStream_t stream);
+
+// Top-p sampling of bf16 rows with one thread-block cluster per row (an alternative
+// decomposition, selectable per handle): per batch of at most batch_rows rows, one kernel that turns every row into a short list of
+// records in `scratch` (topp_cluster_scratch_bytes) and one that replays them and draws the
+// token. Rows that cannot be decided this way are appended to retry_rows (their count in
+// *retry_count) with their rng state and output untouched; the caller then runs
+// launch_sample_rows with that list on the same stream. *retry_count must be zero when the
+// first kernel starts; *retry_count_next is cleared for the call after this one.
 constexpr int kClusterMinVocab = 256;
 bool topp_cluster_supported(int dtype, const void* logits, int64_t rows, int vocab, int64_t row_stride,
                             float inv_t, float topp, int topk);
+size_t topp_cluster_scratch_bytes(int vocab, int64_t batch_rows);
 cudaError_t launch_topp_cluster(
     const void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
     unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, const ExpTable& table,
-    int* retry_rows, int* retry_count, int* retry_count_next, cudaStream_t stream);
+    void* scratch, int64_t batch_rows, int* retry_rows, int* retry_count, int* retry_count_next,
+    cudaStream_t stream);
 
 // temperature == 0: greedy argmax of every row.
 cudaError_t launch_argmax_rows(

@@ -81,8 +81,8 @@ class Sampler:
         _lib.check(_lib.load().etb200_sampler_set_topk(self._h, topk))
 
     def set_kernel_choice(self, choice: int) -> None:
-        """0: the cluster-per-row top-p kernel where it applies (default); 1: always the
-        one-block-per-row kernel. Both return the same tokens."""
+        """0 (default): estimate-guided exact sum for 16-bit logits; 1: the kernel without it;
+        2: the cluster-per-row kernels where they apply. All return the same tokens."""
         _lib.check(_lib.load().etb200_sampler_set_kernel_choice(self._h, choice))
 
     @property
@@ -97,7 +97,7 @@ class Sampler:
 
     @property
     def last_retry_count(self) -> int:
-        """Rows of the most recent top-p call that the cluster kernel handed to the
+        """Rows of the most recent sampling call that the fast kernel handed to the plain
         one-block-per-row kernel (synchronises)."""
         out = C.c_int32(0)
         _lib.check(_lib.load().etb200_sampler_last_retry_count(self._h, C.byref(out)))
@@ -198,6 +198,10 @@ class Sampler:
             self._h, C.c_void_p(logits.data_ptr() if rows else 0), _dtype_code(logits), rows,
             logits.stride(0) if rows else 0, states_ptr, dst, marks, len(dest_ptrs), rank, dest_offset,
             epoch, self._stream()))
+
+    def set_wait_limit(self, seconds: float) -> None:
+        """Limit of the in-kernel wait of ``sample_rows_exchange`` for the other ranks."""
+        _lib.check(_lib.load().etb200_sampler_set_wait_limit_ns(self._h, C.c_uint64(int(seconds * 1e9))))
 
     @property
     def status(self) -> int:

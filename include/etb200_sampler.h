@@ -138,14 +138,20 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_scatter(
  * for every q: once the launch has completed on `stream`, this rank's buffer holds the ids
  * of all ranks for this epoch. Every rank must make the call with the same epoch, which must
  * grow from call to call (1, 2, 3, ...); a rank with rows == 0 still calls. The wait is
- * limited to about a second; if it runs out the launch ends and etb200_sampler_get_status
- * reports 2 (ids of the missing ranks are then stale). Ranks must be distinct GPUs: two such
- * launches never wait for each other on one GPU. */
+ * limited (one second of the GPU's global timer unless etb200_sampler_set_wait_limit_ns says
+ * otherwise); if it runs out the launch ends normally, etb200_sampler_get_status reports 2 and
+ * the ids of the missing ranks are stale: check the status before trusting a buffer. Ranks
+ * must be distinct GPUs: two such launches never wait for each other on one GPU. A handle's
+ * exchange launches must not overlap each other (they share one block counter). */
 ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_exchange(
     etb200_sampler_t* handle, const void* logits_device, int32_t dtype, int64_t rows,
     int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,
     uint64_t* const* arrive_marks, int32_t n_dest, int32_t my_rank, int64_t dest_offset,
     uint64_t epoch, void* stream);
+
+/* Limit of the in-kernel wait of etb200_sampler_sample_rows_exchange, in nanoseconds
+ * (1 microsecond to 60 seconds; default one second). */
+ETB200_EXPORT etb200_error_t etb200_sampler_set_wait_limit_ns(etb200_sampler_t* handle, uint64_t nanoseconds);
 
 /* Reads and clears the handle's device status word (synchronises): 0 = nothing to report,
  * 2 = the arrival wait of etb200_sampler_sample_rows_exchange ran out for some rank. */
@@ -191,16 +197,19 @@ ETB200_EXPORT const char* etb200_static_last_error_message(void);
 ETB200_EXPORT etb200_error_t etb200_selftest_expf(
     const float* x_device, float* y_device, int64_t n, void* stream);
 
-/* Which top-p kernel a handle uses (a tuning and testing knob; no counterpart in the
- * reference). 0 (default): bf16 rows whose starts are 16-byte aligned, with 256 <= vocab_size
- * <= 262144, temperature > 0 and no top-k, are sampled by the kernel that gives every row a
- * thread-block cluster; any row it cannot decide, and every other case, goes to the kernel
- * that gives every row one thread block. 1: always the latter. Both return the same tokens. */
+/* Which sampling kernel a handle uses for temperature != 0 (a tuning and testing knob; no
+ * counterpart in the reference). All choices return the same tokens.
+ *   0 (default): 16-bit logits go through the kernel variant that forms the exact softmax sum
+ *      from estimate-guided integer increments; the rare row it cannot decide, and fp32
+ *      logits, go through the variant without it.
+ *   1: always the variant without it.
+ *   2: top-p on bf16 rows whose starts are 16-byte aligned, with 256 <= vocab_size <= 262144,
+ *      temperature > 0 and no top-k, goes through the pair of kernels that gives every row a
+ *      thread-block cluster; everything else as 0. */
 ETB200_EXPORT etb200_error_t etb200_sampler_set_kernel_choice(etb200_sampler_t* handle, int32_t choice);
 
 /* Diagnostic (synchronises the device): how many rows of the handle's most recent top-p call
- * the cluster kernel left undecided and handed to the one-block-per-row kernel. 0 when the
- * cluster kernel was not used. */
+ * the fast kernel left undecided and handed to the plain one-block-per-row kernel. */
 ETB200_EXPORT etb200_error_t etb200_sampler_last_retry_count(etb200_sampler_t* handle, int32_t* out_count);
 
 /* Number of kernels this library has launched through `handle` so far. */

@@ -15,8 +15,8 @@ using namespace etb200;
 
 extern "C" {
 
-// stats[0] events in all, [1] chunks with two or more open binades in all, [2] largest event
-// count of a slice, [3] largest such chunk count of a slice, [4] chunks with an exact half-way term.
+// stats[0] events in all, [1] staged chunks in all, [2] largest event count of a slice,
+// [3] largest staged count of a slice, [4] chunks whose summary depends on the parity of the significand.
 // Returns 1 when the walk decided the sum (then *sum is it), 0 when it did not, -1 when the
 // event list overflowed (the kernel takes the other route in both of the latter cases).
 int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float perturb, float* sum,
@@ -24,6 +24,7 @@ int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float pertu
   const long slice_len = ((n + (long)n_slices * kCTerms - 1) / ((long)n_slices * kCTerms)) * kCTerms;
   std::vector<ChunkEvent> events(ev_cap);
   std::vector<int> n_events(n_slices, 0), first_event(n_slices, 0);
+  std::vector<float> pool;  // staged chunks, kCTerms floats each
   int total = 0;  // records handed out so far (the kernel: one atomic add per slice)
   bool overflow = false;
   double prefix = 0.0;  // the estimate: a plain double sum, optionally perturbed
@@ -51,12 +52,11 @@ int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float pertu
       chunk_binades(p_in, p_out, binade_margin(base + (long)(c + 1) * kCTerms), &klo, &khi);
       SeqSummary lo, hi;
       bool tie;
-      unsigned flags = summarise_chunk(t, klo, khi, &lo, &hi, &tie);
+      unsigned flags = summarise_chunk(t, [&](int j) { return t[j]; }, klo, khi, &lo, &hi, &tie);
       const bool zero = csum == 0.0;
       if (zero) flags = kEvLo | kEvHi | kEvZero;
-      const bool wild = flags == 0u;
-      const bool unsafe = !zero && (flags & kEvHi) != 0u;
-      const bool event = c == 0 || klo != prev_klo || wild || unsafe || tie;
+      const bool staged = !zero && flags != kEvLo;  // no summary, or two open binades
+      const bool event = c == 0 || klo != prev_klo || staged || tie;
       prev_klo = klo;
       if (tie) ++stats[4];
       if (!event) {
@@ -71,15 +71,20 @@ int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float pertu
       r.a1hi = hi.a1;
       r.xbefore = x;
       r.klo = (short)klo;
-      r.chunk = (short)c;
+      r.pool = -1;
       r.flags = (unsigned short)flags;
-      if (wild || unsafe) ++np;
+      if (staged) {
+        r.pool = (short)(pool.size() / kCTerms);
+        pool.insert(pool.end(), t, t + kCTerms);
+        ++np;
+      }
       if (total + ne < ev_cap) events[total + ne] = r; else overflow = true;
       ++ne;
     }
     ChunkEvent tail;
     memset(&tail, 0, sizeof(tail));
     tail.xbefore = x;
+    tail.pool = -1;
     tail.flags = (unsigned short)kEvTail;
     if (total + ne < ev_cap) events[total + ne] = tail; else overflow = true;
     ++ne;
@@ -91,10 +96,8 @@ int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float pertu
     if (np > stats[3]) stats[3] = np;
   }
   if (overflow) return -1;
-  auto terms = [&](int sl, int chunk, int j) {
-    const long i = (long)sl * slice_len + (long)chunk * kCTerms + j;
-    return i < n ? e[i] : 0.0f;
-  };
+  if (pool.size() / kCTerms > 32767) return -1;
+  auto terms = [&](int slot, int j) { return pool[(size_t)slot * kCTerms + j]; };
   return walk_events(events.data(), first_event.data(), n_events.data(), n_slices, ev_cap, terms, sum) ? 1 : 0;
 }
 

@@ -65,3 +65,48 @@ def test_all_ranks_end_with_all_ids(world, total_rows):
     assert all(ok for _, ok, _ in results)
     spans = sorted(sp for _, _, sp in results)
     assert spans[0][0] == 0 and spans[-1][0] + spans[-1][1] == total_rows
+
+
+def _late_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import time
+    from executorch_b200.sharded import ExchangeTimeout
+    total_rows = 8
+    logits = torch.zeros((total_rows, 4))
+    states = torch.arange(total_rows, dtype=torch.int64)
+    if rank == 0:
+        sh = ShardedSampler(_fake_local_sample, total_rows, deadline_s=1.5)
+        t0 = time.time()
+        try:
+            sh.sample_rows(logits[sh.start:sh.start + sh.count], states[sh.start:sh.start + sh.count])
+            q.put((rank, "returned", time.time() - t0))
+        except ExchangeTimeout:
+            q.put((rank, "timeout", time.time() - t0))
+    else:
+        # this rank never joins the exchange: it fails on the host, between steps
+        time.sleep(4.0)
+        q.put((rank, "absent", 0.0))
+    # the process group is not usable after an abandoned collective: leave without the
+    # collective teardown (once the result is on its way)
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_a_rank_that_never_arrives_ends_the_exchange_with_an_error():
+    """Failure detection on the host: rank 1 never calls the exchange; rank 0's deadline turns
+    the wait into ExchangeTimeout instead of blocking."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29000 + (os.getpid() % 500) + 431
+    procs = [ctx.Process(target=_late_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict((r, (what, dt)) for r, what, dt in (q.get(timeout=120) for _ in range(2)))
+    for p in procs:
+        p.join(timeout=60)
+    assert results[0][0] == "timeout", results
+    assert 1.0 <= results[0][1] < 4.0, results
+    assert results[1][0] == "absent"
