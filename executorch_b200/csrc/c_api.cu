@@ -51,8 +51,8 @@ struct etb200_sampler {
   size_t cluster_scratch_bytes = 0;
   unsigned retry_parity = 0;
   unsigned long long wait_ns = 1000000000ull;  // limit of the in-kernel wait for the other ranks
-  // 0: the estimate-guided variant for 16-bit logits; 1: always the variant without it;
-  // 2: the cluster-per-row kernels where they apply, else as 0
+  // 0: automatic; 1: the one-block-per-row kernel; 2: the cluster-per-row kernels where they
+  // apply; 3: the one-block-per-row kernel with the estimate-guided sum for 16-bit logits
   int kernel_choice = 0;
   int guided_blocks_per_sm[2] = {0, 0};
 };
@@ -264,10 +264,14 @@ etb200_error_t sample_rows_device(
     etb200_error_t err = ensure_scratch(h, blocks);
     if (err != ETB200_OK) return err;
   }
-  const bool want_cluster = h->kernel_choice == 2 &&
-                            topp_cluster_supported(dtype, logits, rows, h->vocab, row_stride, h->inv_temperature,
-                                                   h->topp, topk);
-  const bool want_guided = !want_cluster && h->kernel_choice != 1 && guided_supported(dtype);
+  // Automatic choice, from measurements on B200: the cluster pair is the quickest way to one
+  // token from one long row (batch-1 decode); from a handful of rows on, one block per row
+  // keeps more rows in flight and wins.
+  const bool cluster_ok = topp_cluster_supported(dtype, logits, rows, h->vocab, row_stride, h->inv_temperature,
+                                                 h->topp, topk);
+  const bool want_cluster =
+      cluster_ok && (h->kernel_choice == 2 || (h->kernel_choice == 0 && rows == 1 && h->vocab >= 65536));
+  const bool want_guided = !want_cluster && h->kernel_choice == 3 && guided_supported(dtype);
   if (want_cluster || want_guided) {
     // Two launches: the fast kernel(s) take every row; the rows they leave undecided (rare) are
     // then sampled by the plain one-block-per-row kernel, which also carries the arrival
@@ -390,7 +394,7 @@ etb200_error_t etb200_sampler_set_wait_limit_ns(etb200_sampler_t* h, uint64_t na
 
 etb200_error_t etb200_sampler_set_kernel_choice(etb200_sampler_t* h, int32_t choice) {
   ETB_CHECK_ARG(h != nullptr, "handle is null");
-  ETB_CHECK_ARG(choice >= 0 && choice <= 2, "choice must be 0, 1 or 2, got %d", choice);
+  ETB_CHECK_ARG(choice >= 0 && choice <= 3, "choice must be 0, 1, 2 or 3, got %d", choice);
   h->kernel_choice = choice;
   return ETB200_OK;
 }

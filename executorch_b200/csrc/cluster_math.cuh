@@ -46,6 +46,11 @@ constexpr unsigned kEvTail = 1u;  // closes the list of one slice: carries only 
 constexpr unsigned kEvLo = 2u;    // (a0lo, a1lo) summarise the chunk in binade klo
 constexpr unsigned kEvHi = 4u;    // (a0hi, a1hi) summarise the chunk in binade klo + 1
 constexpr unsigned kEvZero = 8u;  // every term of the chunk is zero: it changes no sum
+// The chunk holds an exact half-way term for binade klo / klo + 1: its increment depends on the
+// parity of the running significand. The chunk is staged, and resolve_tie_event() forms the
+// two-parity summary from the staged terms before the walk (many such chunks side by side).
+constexpr unsigned kEvTieLo = 16u;
+constexpr unsigned kEvTieHi = 32u;
 
 // One event chunk as the walk sees it. `xbefore` is the sum of the integer increments of the
 // non-event chunks of the same slice in front of this chunk (event chunks contribute 0), so
@@ -53,7 +58,7 @@ constexpr unsigned kEvZero = 8u;  // every term of the chunk is zero: it changes
 // chunks between them; that run is summarised in the binade klo of the event in front of it
 // (a chunk whose binade differs from its predecessor's is always an event). `pool` is the slot
 // in which the chunk's 32 terms are staged for the walk (chunks that may have to be added term
-// by term: two open binades, or no summary at all), or -1.
+// by term, or whose summary is still pending), or -1.
 struct alignas(16) ChunkEvent {
   int a0lo, a1lo, a0hi, a1hi;
   unsigned long long xbefore;
@@ -109,42 +114,45 @@ ETB_HD int chunk_increment_fast(const Arr& e, int k, bool* half) {
 }
 
 // The general two-parity summary of a chunk in binade k (27 <= k <= 252), term by term in row
-// order: `at(j)` returns term j. Used for the rare chunk that holds an exact half-way term.
-template <typename At>
-ETB_HD SeqSummary chunk_summary_exact(At at, int k) {
+// order.
+ETB_HD SeqSummary chunk_summary_exact(const float* terms, int k) {
   SeqSummary s;
   seq_identity(&s);
   const float inv_u = seq_inv_u(k);
-  for (int j = 0; j < kCTerms; ++j) seq_push_scaled(&s, at(j), inv_u);
+  for (int j = 0; j < kCTerms; ++j) seq_push_scaled(&s, terms[j], inv_u);
   return s;
 }
 
-// Summaries of one chunk for its open binades: `e` holds the terms in any order (the tie-free
-// increments are sums of integers), `at(j)` returns them in row order. Returns the kEvLo /
-// kEvHi flags (0 for a chunk with more than two open binades, which has to be staged and added
-// term by term); *tie is set when a summary depends on the parity of the running significand.
-template <typename Arr, typename At>
-ETB_HD unsigned summarise_chunk(const Arr& e, At at, int klo, int khi, SeqSummary* lo, SeqSummary* hi,
-                                bool* tie) {
-  seq_identity(lo);
-  seq_identity(hi);
-  *tie = false;
+// What one thread decides about its chunk from the tie-free increments: the flags of the
+// chunk's record. `half_lo` / `half_hi`: chunk_increment_fast met an exact half-way term.
+ETB_HD unsigned chunk_flags(int klo, int khi, bool half_lo, bool half_hi) {
   if (!chunk_summarisable(klo, khi)) return 0u;
-  bool half;
-  const int inc = chunk_increment_fast(e, klo, &half);
-  lo->a0 = lo->a1 = inc;
-  if (half) {
-    *lo = chunk_summary_exact(at, klo);
-    if (lo->a0 != lo->a1) *tie = true;
+  unsigned f = half_lo ? kEvTieLo : kEvLo;
+  if (khi != klo) f |= half_hi ? kEvTieHi : kEvHi;
+  return f;
+}
+
+// A chunk is an ordinary one (its increment simply adds to the run it is in) when it has one
+// open binade and a tie-free summary for it; everything else is staged.
+ETB_HD bool chunk_is_staged(unsigned flags) { return (flags & kEvZero) == 0u && flags != kEvLo; }
+
+// Replaces the pending (kEvTieLo / kEvTieHi) summaries of one event by the exact two-parity
+// summaries formed from its staged terms (row order). One thread per event.
+ETB_HD void resolve_tie_event(ChunkEvent* ev, const float* terms) {
+  unsigned f = ev->flags;
+  if (f & kEvTieLo) {
+    const SeqSummary s = chunk_summary_exact(terms, ev->klo);
+    ev->a0lo = s.a0;
+    ev->a1lo = s.a1;
+    f = (f & ~kEvTieLo) | kEvLo;
   }
-  if (khi == klo) return kEvLo;
-  const int inc_hi = chunk_increment_fast(e, khi, &half);
-  hi->a0 = hi->a1 = inc_hi;
-  if (half) {
-    *hi = chunk_summary_exact(at, khi);
-    if (hi->a0 != hi->a1) *tie = true;
+  if (f & kEvTieHi) {
+    const SeqSummary s = chunk_summary_exact(terms, ev->klo + 1);
+    ev->a0hi = s.a0;
+    ev->a1hi = s.a1;
+    f = (f & ~kEvTieHi) | kEvHi;
   }
-  return kEvLo | kEvHi;
+  ev->flags = (unsigned short)f;
 }
 
 // The sequential replay. `events` holds the records of all slices; slice sl owns the

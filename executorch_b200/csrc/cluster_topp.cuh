@@ -124,17 +124,6 @@ __device__ __forceinline__ void cluster_terms8(const ClusterShared& sm, const ui
   }
 }
 
-#if defined(ETB200_PHASE_CLOCKS)
-// Debug build only: clock64 stamps of block 0 / row 0, one per phase boundary.
-__device__ long long g_phase_clock[16];
-#define ETB_STAMP(k)                                                        \
-  do {                                                                      \
-    if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] = clock64();  \
-  } while (0)
-#else
-#define ETB_STAMP(k)
-#endif
-
 __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     const unsigned short* __restrict__ logits, int vocab, int64_t row_stride, int slice_len, float inv_t,
     float topp, ExpTable table, SliceScratch* __restrict__ scratch) {
@@ -283,11 +272,8 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
   const float cutoff = __fdiv_rn(__fsub_rn(1.0f, topp), (float)(vocab - 1));
   const float e_floor = fmaxf(cutoff * 0.999999f, kGuessFloor);
   int klo = 1, khi = 1;
-  SeqSummary slo, shi;
-  seq_identity(&slo);
-  seq_identity(&shi);
+  int inc_lo = 0, inc_hi = 0;
   unsigned flags = 0u;
-  bool tie = false;
   if (active) chunk_binades(p_in, p_out, binade_margin((long long)i0 + (long long)(tid + 1) * kCTerms), &klo, &khi);
   const bool can_sum = active && chunk_summarisable(klo, khi);
   const bool two = can_sum && khi != klo;
@@ -326,49 +312,24 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     const float top = fmaxf(fmaxf(gmax[0], gmax[1]), fmaxf(gmax[2], gmax[3]));
     if (__fsub_rn(__fmul_rn(top, inv_t), mx) < -0x1.9fe368p6f) {
       flags = kEvLo | kEvHi | kEvZero;
-    } else if (can_sum) {
+    } else {
       const float tlo = acc_lo[0] + acc_lo[1], thi = acc_hi[0] + acc_hi[1];
-      slo.a0 = slo.a1 = (int)(tlo < 33554432.0f ? tlo : 33554432.0f);
-      flags = kEvLo;
-      bool half_lo = !(md_lo < 0.5f), half_hi = false;
-      if (two) {
-        shi.a0 = shi.a1 = (int)(thi < 33554432.0f ? thi : 33554432.0f);
-        half_hi = !(md_hi < 0.5f);
-        flags = kEvLo | kEvHi;
-      }
-      if (half_lo || half_hi) {
-        // rare: an exact half-way term; the two-parity summary needs the terms in row order
-        float ord[kCTerms];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float e[8];
-          cluster_terms8(sm, raw[q], inv_t, mx, e);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ord[((q ^ sw) << 3) + j] = e[j];
-        }
-        const float* po = ord;
-        if (half_lo) {
-          slo = chunk_summary_exact([po](int j) { return po[j]; }, klo);
-          tie = tie || slo.a0 != slo.a1;
-        }
-        if (half_hi) {
-          shi = chunk_summary_exact([po](int j) { return po[j]; }, khi);
-          tie = tie || shi.a0 != shi.a1;
-        }
-      }
+      inc_lo = (int)(tlo < 33554432.0f ? tlo : 33554432.0f);
+      inc_hi = two ? (int)(thi < 33554432.0f ? thi : 33554432.0f) : 0;
+      // a chunk with an exact half-way term is staged; the finishing kernel forms its summary
+      flags = chunk_flags(klo, khi, !(md_lo < 0.5f), two && !(md_hi < 0.5f));
     }
   }
   ETB_STAMP(4);
-  const bool zero = (flags & kEvZero) != 0u;
-  const bool staged = active && !zero && flags != kEvLo;  // two open binades, or no summary
+  const bool staged = active && chunk_is_staged(flags);
   // a chunk whose binade differs from its predecessor's is an event; so is the first of a slice
   int prev_klo = __shfl_up_sync(0xffffffffu, klo, 1);
   if (lane == 31) sm.wklo[warp] = klo;
   __syncthreads();  // also: every candidate of this slice is in sm.lcand
   if (lane == 0) prev_klo = warp > 0 ? sm.wklo[warp - 1] : -1;
-  const bool event = active && (tid == 0 || klo != prev_klo || staged || tie);
+  const bool event = active && (tid == 0 || klo != prev_klo || staged);
   // exclusive scans over the block: increments of the ordinary chunks, and event slots
-  const unsigned inc_mine = (active && !event) ? (unsigned)slo.a0 : 0u;  // < 2^24 for a valid run
+  const unsigned inc_mine = (active && !event) ? (unsigned)inc_lo : 0u;  // < 2^24 for a valid run
   unsigned inc_incl = inc_mine;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
@@ -417,10 +378,8 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
         }
       }
       ChunkEvent rec;
-      rec.a0lo = slo.a0;
-      rec.a1lo = slo.a1;
-      rec.a0hi = shi.a0;
-      rec.a1hi = shi.a1;
+      rec.a0lo = rec.a1lo = inc_lo;
+      rec.a0hi = rec.a1hi = inc_hi;
       rec.xbefore = x_pre + (unsigned long long)(inc_incl - inc_mine);
       rec.klo = (short)klo;
       rec.pool = (short)(staged ? slot : -1);
@@ -563,14 +522,32 @@ __global__ void __launch_bounds__(kFThreads) topp_finish_kernel(
       __syncthreads();
     }
     ETB_STAMP(7);
-    // ---- the exact sequential sum, replayed by one thread
+    // The slices' records become one list: a slice's closing record carries the increment of
+    // its trailing run, so adding the totals of the slices in front makes `xbefore` run on,
+    // and every closing record but the last turns into an empty record of the run it closes.
     if (tid == 0) {
+      unsigned long long base = 0ull;
+      for (int s = 0; s < csize; ++s) {
+        const int e0 = sm.ev_first[s], ne = sm.ev_count[s];
+        for (int i = 0; i < ne; ++i) sm.w.events[e0 + i].xbefore += base;
+        base = sm.w.events[e0 + ne - 1].xbefore;
+      }
+    }
+    __syncthreads();
+    // ---- pending two-parity summaries: one thread per event, side by side
+    for (int i = tid; i < n_ev; i += kFThreads) {
+      ChunkEvent* e = &sm.w.events[i];
+      if ((e->flags & (kEvTieLo | kEvTieHi)) != 0u && e->pool >= 0) resolve_tie_event(e, sm.w.pool[e->pool]);
+    }
+    __syncthreads();
+    // ---- the exact sequential sum, replayed by one warp
+    if (warp == 0) {
       float s = 0.0f;
-      const float(*pool)[kCTerms] = sm.w.pool;
-      const bool ok = walk_events(sm.w.events, sm.ev_first, sm.ev_count, csize, kFEventCap,
-                                  [pool](int slot, int j) { return pool[slot][j]; }, &s);
-      sm.sum = s;
-      sm.ok = ok ? 1 : 0;
+      const bool ok = walk_events_warp(sm.w.events, n_ev, sm.w.pool, kFPoolCap, &s);
+      if (lane == 0) {
+        sm.sum = s;
+        sm.ok = ok ? 1 : 0;
+      }
     }
     __syncthreads();
     decided = sm.ok != 0;

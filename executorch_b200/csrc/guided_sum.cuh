@@ -18,6 +18,17 @@
 // Returns false when the replay could not decide (a list overflowed, or an assumption about
 // the estimate did not hold): the caller hands the row to the kernel without this pass.
 
+#if defined(ETB200_PHASE_CLOCKS)
+// Debug build only: clock64 stamps of block 0 / row 0, one per phase boundary.
+__device__ long long g_phase_clock[16];
+#define ETB_STAMP(k)                                                        \
+  do {                                                                      \
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] = clock64();  \
+  } while (0)
+#else
+#define ETB_STAMP(k)
+#endif
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -104,6 +115,115 @@ __device__ __forceinline__ unsigned short neg_inf_bits() {
   return std::is_same<T, __nv_bfloat16>::value ? (unsigned short)0xFF80u : (unsigned short)0xFC00u;
 }
 
+// The replay of walk_events() by one warp: the lanes take 32 consecutive event records at a
+// time, a warp scan applies every record in front of the first one that needs more than an
+// integer addition (a chunk that leaves the binade, one that has no summary for the current
+// binade, one whose increment depends on parity), and that one is then handled by all lanes in
+// step, exactly as walk_events() handles it. One slice (`n_ev` records, the last one kEvTail).
+// Same result as walk_events(): the exact sum, or false.
+__device__ bool walk_events_warp(const ChunkEvent* ev, int n_ev, const float (*pool)[kCTerms], int pool_cap,
+                                 float* sum) {
+  const int lane = threadIdx.x & 31;
+  int k = 1, n = 0;   // the running sum as (binade, significand); warp-uniform
+  int run_k = -1;     // binade of the ordinary chunks behind the last record that was applied
+  unsigned long long x_prev = 0ull;
+  int pos = 0;
+  while (pos < n_ev) {
+    const int i = pos + lane;
+    const bool valid = i < n_ev;
+    ChunkEvent r = ev[valid ? i : n_ev - 1];
+    unsigned long long xb_prev = __shfl_up_sync(0xffffffffu, r.xbefore, 1);
+    int klo_prev = __shfl_up_sync(0xffffffffu, (int)r.klo, 1);
+    if (lane == 0) {
+      xb_prev = x_prev;
+      klo_prev = run_k;
+    }
+    const unsigned long long gap = r.xbefore - xb_prev;
+    const bool tail = (r.flags & kEvTail) != 0u, zero = (r.flags & kEvZero) != 0u;
+    int a0 = 0;
+    bool have = false;
+    if ((r.flags & kEvLo) && k == r.klo) {
+      have = r.a0lo == r.a1lo;
+      a0 = r.a0lo;
+    } else if ((r.flags & kEvHi) && k == r.klo + 1) {
+      have = r.a0hi == r.a1hi;
+      a0 = r.a0hi;
+    }
+    // a record is simple when an integer addition applies it in the current binade
+    const bool simple = valid && gap < (unsigned long long)kSeqLimit && (gap == 0ull || klo_prev == k) &&
+                        (tail || zero || have);
+    const unsigned inc = simple ? (unsigned)gap + ((tail || zero) ? 0u : (unsigned)a0) : 0u;  // < 2^26
+    unsigned incl = inc;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    const bool stop = !simple || (unsigned)n + incl >= (unsigned)kSeqLimit;  // invalid lanes stop too
+    const unsigned sb = __ballot_sync(0xffffffffu, stop);
+    const int f = sb != 0u ? __ffs(sb) - 1 : 32;  // records in front of lane f are applied
+    if (f > 0) {
+      n += (int)__shfl_sync(0xffffffffu, incl, f - 1);
+      x_prev = __shfl_sync(0xffffffffu, r.xbefore, f - 1);
+      // the binade of the following run: that of the last record applied (a closing record has none)
+      const int kl = __shfl_sync(0xffffffffu, (int)r.klo, f - 1);
+      const unsigned fl = __shfl_sync(0xffffffffu, (unsigned)r.flags, f - 1);
+      if ((fl & kEvTail) == 0u) run_k = kl;
+      pos += f;
+    }
+    // the record at pos, if any, needs the long way; so do wild records right behind it
+    while (pos < n_ev) {
+      const ChunkEvent q = ev[pos];
+      const unsigned long long g2 = q.xbefore - x_prev;
+      if (g2 != 0ull) {
+        if (run_k != k || g2 >= (unsigned long long)kSeqLimit) return false;
+        n += (int)g2;
+        if (n >= kSeqLimit) return false;
+      }
+      x_prev = q.xbefore;
+      ++pos;
+      if (q.flags & kEvTail) break;
+      run_k = q.klo;
+      if (q.flags & kEvZero) break;
+      SeqSummary sm2;
+      bool have2 = false;
+      if ((q.flags & kEvLo) && k == q.klo) {
+        sm2.a0 = q.a0lo;
+        sm2.a1 = q.a1lo;
+        have2 = true;
+      } else if ((q.flags & kEvHi) && k == q.klo + 1) {
+        sm2.a0 = q.a0hi;
+        sm2.a1 = q.a1hi;
+        have2 = true;
+      }
+      if (have2) {
+        const int n2 = seq_apply(n, sm2);
+        if (n2 < kSeqLimit) {
+          n = n2;
+          break;
+        }
+      }
+      // the chunk leaves the binade (or has no summary for it): real float additions
+      if (q.pool < 0 || q.pool >= pool_cap) return false;
+      const float4* t4 = reinterpret_cast<const float4*>(pool[q.pool]);
+      float s = seq_value(k, n);
+#pragma unroll
+      for (int j = 0; j < kCTerms / 4; ++j) {
+        const float4 t = t4[j];
+        s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, t.x), t.y), t.z), t.w);
+      }
+      if (!(s < 3.0e38f)) return false;
+      k = seq_kb(s);
+      n = seq_n(s);
+      // the start of a row is a run of such chunks: take the next one directly
+      if (pos < n_ev && ev[pos].flags == 0u && ev[pos].xbefore == x_prev) continue;
+      break;
+    }
+  }
+  *sum = seq_value(k, n);
+  return true;
+}
+
 template <typename T, typename S>
 __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_parity, bool use_list,
                                 float e_floor, Entry* listA, int* n_a_out, float* sum_out) {
@@ -114,6 +234,11 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
   const int n_tiles = (vocab + kGTile - 1) / kGTile;
   const unsigned short* row16 = reinterpret_cast<const unsigned short*>(rm.row);
   unsigned short* tile = reinterpret_cast<unsigned short*>(sm.u.stage);
+  // the chunks' open binades: tiles 0..7 in g.kb, tiles 8..15 behind the tile buffer (the union
+  // member is 40 KB, the tile 32 KB)
+  unsigned short* kb_hi = tile + kGTile;
+  static_assert(sizeof(sm.u.stage) >= (size_t)kGTile * 2 + (size_t)(kGMaxTiles - 8) * kThreads * 2,
+                "the union buffer must hold a tile and the upper half of the binade table");
   const int sw = (tid >> 1) & 3;  // register group q holds the chunk's logits (q ^ sw) * 8 ...
   const float inv_t = rm.inv_t, mx = rm.mx;
   bool copies_ok = true;
@@ -150,7 +275,13 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
   // Waits for tile r and loads this thread's chunk of it (four 128-bit reads, rotated per
   // thread pair so that a warp's reads fall into distinct banks).
   auto take_tile = [&](int r, uint4 (&raw)[4], bool& active) {
+#if defined(ETB200_PHASE_CLOCKS)
+    const long long w0 = clock64();
+#endif
     if (!wait_bulk_copy(&g.mbar, copy_parity)) copies_ok = false;
+#if defined(ETB200_PHASE_CLOCKS)
+    if (blockIdx.x == 0 && tid == 0) g_phase_clock[10] += clock64() - w0;
+#endif
     copy_parity ^= 1u;
     if (vocab - r * kGTile < kGTile) __syncthreads();  // the ragged end was written by other threads
     active = r * kThreads + tid < n_chunks;
@@ -161,6 +292,7 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
   };
 
   __syncthreads();  // the buffer (a union member) is free
+  ETB_STAMP(2);
   start_tile(0);
 
   // ---- sweep 1: approximate sums, the binades each chunk can meet
@@ -208,12 +340,13 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
         int klo, khi;
         chunk_binades(p_in, p_out, binade_margin((long long)(r * kThreads + tid + 1) * kCTerms), &klo, &khi);
         const int span = khi - klo < 3 ? khi - klo : 3;
-        g.kb[r][tid] = (unsigned short)(klo | (span << 8));
+        (r < 8 ? g.kb[r] : kb_hi + (r - 8) * kThreads)[tid] = (unsigned short)(klo | (span << 8));
       }
       base += tile_tot;
     }
   }
 
+  ETB_STAMP(3);
   // ---- sweep 2: exact terms, candidates, integer increments, event records
   unsigned long long x_run = 0ull;  // increments of the ordinary chunks so far (block-uniform)
   int ev_n = 0, st_n = 0, n_a = 0;  // events, staged chunks, candidates so far (block-uniform)
@@ -228,7 +361,7 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
     take_tile(r, raw, active);
     int klo = 1, khi = 1;
     if (active) {
-      const unsigned kbv = g.kb[r][tid];
+      const unsigned kbv = (r < 8 ? g.kb[r] : kb_hi + (r - 8) * kThreads)[tid];
       klo = (int)(kbv & 0xFFu);
       khi = klo + (int)(kbv >> 8);
     }
@@ -236,11 +369,8 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
     const bool two = can_sum && khi != klo;
     // the second binade is summed by the whole warp whenever one of its chunks needs it
     const bool warp_two = __any_sync(0xffffffffu, two);
-    SeqSummary slo, shi;
-    seq_identity(&slo);
-    seq_identity(&shi);
+    int inc_lo = 0, inc_hi = 0;
     unsigned flags = 0u, cmask = 0u;
-    bool tie = false;
     if (active) {
       const float inv_lo = seq_inv_u(can_sum ? klo : 127), inv_hi = seq_inv_u(can_sum ? khi : 127);
       float acc_lo[2] = {0.0f, 0.0f}, acc_hi[2] = {0.0f, 0.0f};
@@ -264,49 +394,23 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
       // a chunk whose largest logit already gives e = 0 holds nothing but zeros
       if (__fsub_rn(__fmul_rn(top, inv_t), mx) < -0x1.9fe368p6f) {
         flags = kEvLo | kEvHi | kEvZero;
-      } else if (can_sum) {
+      } else {
         const float tlo = acc_lo[0] + acc_lo[1], thi = acc_hi[0] + acc_hi[1];
-        slo.a0 = slo.a1 = (int)(tlo < 33554432.0f ? tlo : 33554432.0f);
-        flags = kEvLo;
-        const bool half_lo = !(md_lo < 0.5f);
-        bool half_hi = false;
-        if (two) {
-          shi.a0 = shi.a1 = (int)(thi < 33554432.0f ? thi : 33554432.0f);
-          half_hi = !(md_hi < 0.5f);
-          flags = kEvLo | kEvHi;
-        }
-        if (half_lo || half_hi) {
-          // rare: an exact half-way term; the two-parity summary needs the terms in row order
-          float ord[kCTerms];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float e[8];
-            terms8(rm, sm, raw[q], e);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ord[((q ^ sw) << 3) + j] = e[j];
-          }
-          const float* po = ord;
-          if (half_lo) {
-            slo = chunk_summary_exact([po](int j) { return po[j]; }, klo);
-            tie = tie || slo.a0 != slo.a1;
-          }
-          if (half_hi) {
-            shi = chunk_summary_exact([po](int j) { return po[j]; }, khi);
-            tie = tie || shi.a0 != shi.a1;
-          }
-        }
+        inc_lo = (int)(tlo < 33554432.0f ? tlo : 33554432.0f);
+        inc_hi = two ? (int)(thi < 33554432.0f ? thi : 33554432.0f) : 0;
+        // a chunk with an exact half-way term is staged; its summary is formed after the sweep
+        flags = chunk_flags(klo, khi, !(md_lo < 0.5f), two && !(md_hi < 0.5f));
       }
     }
-    const bool zero = (flags & kEvZero) != 0u;
-    const bool staged = active && !zero && flags != kEvLo;  // two open binades, or no summary
+    const bool staged = active && chunk_is_staged(flags);
     int prev_klo = __shfl_up_sync(0xffffffffu, klo, 1);
     if (lane == 31) g.wklo[r & 1][warp] = klo;
     __syncthreads();  // every thread holds its chunk of tile r; the warps' last binades are visible
     if (r + 1 < n_tiles) start_tile(r + 1);
     // a chunk whose binade differs from its predecessor's is an event; so is the row's first
     if (lane == 0) prev_klo = warp > 0 ? g.wklo[r & 1][warp - 1] : (r > 0 ? g.wklo[(r + 1) & 1][kWarps - 1] : -1);
-    const bool event = active && (klo != prev_klo || staged || tie);
-    const unsigned inc_mine = (active && !event) ? (unsigned)slo.a0 : 0u;  // < 2^24 for a valid run
+    const bool event = active && (klo != prev_klo || staged);
+    const unsigned inc_mine = (active && !event) ? (unsigned)inc_lo : 0u;  // < 2^24 for a valid run
     unsigned inc_incl = inc_mine;
     int cnd_incl = __popc(cmask);
 #pragma unroll
@@ -363,10 +467,8 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
         }
       }
       ChunkEvent rec;
-      rec.a0lo = slo.a0;
-      rec.a1lo = slo.a1;
-      rec.a0hi = shi.a0;
-      rec.a1hi = shi.a1;
+      rec.a0lo = rec.a1lo = inc_lo;
+      rec.a0hi = rec.a1hi = inc_hi;
       rec.xbefore = x_run + x_pre + (unsigned long long)(inc_incl - inc_mine);
       rec.klo = (short)klo;
       rec.pool = (short)slot;
@@ -423,19 +525,25 @@ __device__ bool guided_sum_pass(S& sm, const RowMath<T, S>& rm, uint32_t& copy_p
   }
   __threadfence_block();
   __syncthreads();
-  // ---- replay
-  if (tid == 0) {
-    float s = 0.0f;
-    bool ok = fits && copies_ok;
-    if (ok) {
-      const float(*pool)[kCTerms] = g.pool;
-      ok = walk_events(g.events, g.ev_first, g.ev_count, 1, kGEventCap,
-                       [pool](int slot, int j) { return pool[slot][j]; }, &s);
-    }
-    g.sum = s;
-    g.ok = ok ? 1 : 0;
+  ETB_STAMP(4);
+  // ---- pending two-parity summaries: one thread per event, side by side
+  if (fits && tid < ev_n) {
+    ChunkEvent* e = &g.events[tid];
+    if ((e->flags & (kEvTieLo | kEvTieHi)) != 0u && e->pool >= 0) resolve_tie_event(e, g.pool[e->pool]);
   }
   __syncthreads();
+  // ---- replay, by one warp
+  if (warp == 0) {
+    float s = 0.0f;
+    bool ok = fits && copies_ok;
+    if (ok) ok = walk_events_warp(g.events, ev_n + 1, g.pool, kGPoolCap, &s);
+    if (lane == 0) {
+      g.sum = s;
+      g.ok = ok ? 1 : 0;
+    }
+  }
+  __syncthreads();
+  ETB_STAMP(5);
   *n_a_out = n_a;
   *sum_out = g.sum;
   return g.ok != 0;

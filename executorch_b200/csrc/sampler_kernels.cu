@@ -79,7 +79,7 @@ struct Entry {
 constexpr int kGTile = kThreads * kCTerms;  // logits per tile: one chunk of 32 per thread
 constexpr int kGMaxTiles = 16;
 constexpr int kGEventCap = 256;
-constexpr int kGPoolCap = 80;
+constexpr int kGPoolCap = 112;
 
 struct GuidedShared {
   unsigned long long mbar;  // completion barrier of the tile copies; phases alternate
@@ -95,9 +95,10 @@ struct GuidedShared {
   int wklo[2][kWarps];
   ChunkEvent events[kGEventCap];
   float pool[kGPoolCap][kCTerms];
-  unsigned short kb[kGMaxTiles][kThreads];  // per chunk: lower open binade | (open binades - 1) << 8
+  unsigned short kb[8][kThreads];  // per chunk of tiles 0..7: lower open binade | (open binades - 1) << 8
 };
 struct NoGuidedShared {};
+static_assert(kGEventCap <= kThreads, "one thread per event resolves the pending summaries");
 
 template <bool kLut, bool kGuided = false>
 struct __align__(16) Shared {
@@ -1428,6 +1429,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     rm.sum = 1.0f;
     rm.probs = false;
 
+    ETB_STAMP(0);
     // ---- pass 1: max of the scaled logits
     rm.mx = row_max_scaled<T>(sm, rm.row, vocab, rm.vec_ok, inv_t);
 
@@ -1439,6 +1441,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       sm.misc_f[0] = next_coin(&st_next);
       if constexpr (!kGuided) rng_states[r] = st_next;
     }
+    ETB_STAMP(1);
     if constexpr (kLut) {
       rm.build_lut(sm);  // the previous row's readers are behind the barriers of block_max
     }
@@ -1731,6 +1734,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         token = listB[j].idx;
       }
     }
+    ETB_STAMP(6);
     store_token(out_ids, peers, r, token);
     __syncthreads();
   }

@@ -81,8 +81,8 @@ class Sampler:
         _lib.check(_lib.load().etb200_sampler_set_topk(self._h, topk))
 
     def set_kernel_choice(self, choice: int) -> None:
-        """0 (default): estimate-guided exact sum for 16-bit logits; 1: the kernel without it;
-        2: the cluster-per-row kernels where they apply. All return the same tokens."""
+        """0 (default): automatic; 1: one block per row; 2: a thread-block cluster per row where
+        that applies; 3: one block per row with the estimate-guided sum. Same tokens from all."""
         _lib.check(_lib.load().etb200_sampler_set_kernel_choice(self._h, choice))
 
     @property

@@ -199,13 +199,14 @@ ETB200_EXPORT etb200_error_t etb200_selftest_expf(
 
 /* Which sampling kernel a handle uses for temperature != 0 (a tuning and testing knob; no
  * counterpart in the reference). All choices return the same tokens.
- *   0 (default): 16-bit logits go through the kernel variant that forms the exact softmax sum
- *      from estimate-guided integer increments; the rare row it cannot decide, and fp32
- *      logits, go through the variant without it.
- *   1: always the variant without it.
- *   2: top-p on bf16 rows whose starts are 16-byte aligned, with 256 <= vocab_size <= 262144,
- *      temperature > 0 and no top-k, goes through the pair of kernels that gives every row a
- *      thread-block cluster; everything else as 0. */
+ *   0 (default): automatic -- kernel 2 for a single bf16 row of 65536 logits or more (batch-1
+ *      decode, where it is the quickest), kernel 1 otherwise.
+ *   1: one thread block per row.
+ *   2: a thread-block cluster per row plus a finishing kernel (top-p on bf16 rows whose starts
+ *      are 16-byte aligned, 256 <= vocab_size <= 262144, temperature > 0, no top-k); other
+ *      cases, and rows it cannot decide, fall to kernel 1.
+ *   3: kernel 1 with the exact softmax sum formed from estimate-guided integer increments
+ *      (16-bit logits); rows it cannot decide fall to kernel 1. */
 ETB200_EXPORT etb200_error_t etb200_sampler_set_kernel_choice(etb200_sampler_t* handle, int32_t choice);
 
 /* Diagnostic (synchronises the device): how many rows of the handle's most recent top-p call

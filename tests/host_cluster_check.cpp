@@ -16,7 +16,7 @@ using namespace etb200;
 extern "C" {
 
 // stats[0] events in all, [1] staged chunks in all, [2] largest event count of a slice,
-// [3] largest staged count of a slice, [4] chunks whose summary depends on the parity of the significand.
+// [3] largest staged count of a slice, [4] chunks with an exact half-way term.
 // Returns 1 when the walk decided the sum (then *sum is it), 0 when it did not, -1 when the
 // event list overflowed (the kernel takes the other route in both of the latter cases).
 int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float perturb, float* sum,
@@ -50,25 +50,28 @@ int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float pertu
       const float p_out = (float)(prefix * (1.0 + perturb));
       int klo, khi;
       chunk_binades(p_in, p_out, binade_margin(base + (long)(c + 1) * kCTerms), &klo, &khi);
-      SeqSummary lo, hi;
-      bool tie;
-      unsigned flags = summarise_chunk(t, [&](int j) { return t[j]; }, klo, khi, &lo, &hi, &tie);
+      // as a thread of the kernel: tie-free increments for the open binade(s), then the flags
+      bool half_lo = false, half_hi = false;
+      int inc_lo = 0, inc_hi = 0;
+      if (chunk_summarisable(klo, khi)) {
+        inc_lo = chunk_increment_fast(t, klo, &half_lo);
+        if (khi != klo) inc_hi = chunk_increment_fast(t, khi, &half_hi);
+      }
+      unsigned flags = chunk_flags(klo, khi, half_lo, half_hi);
       const bool zero = csum == 0.0;
       if (zero) flags = kEvLo | kEvHi | kEvZero;
-      const bool staged = !zero && flags != kEvLo;  // no summary, or two open binades
-      const bool event = c == 0 || klo != prev_klo || staged || tie;
+      const bool staged = chunk_is_staged(flags);
+      const bool event = c == 0 || klo != prev_klo || staged;
       prev_klo = klo;
-      if (tie) ++stats[4];
+      if (flags & (kEvTieLo | kEvTieHi)) ++stats[4];
       if (!event) {
-        x += (unsigned long long)lo.a0;
+        x += (unsigned long long)inc_lo;
         continue;
       }
       ChunkEvent r;
       memset(&r, 0, sizeof(r));
-      r.a0lo = lo.a0;
-      r.a1lo = lo.a1;
-      r.a0hi = hi.a0;
-      r.a1hi = hi.a1;
+      r.a0lo = r.a1lo = inc_lo;
+      r.a0hi = r.a1hi = inc_hi;
       r.xbefore = x;
       r.klo = (short)klo;
       r.pool = -1;
@@ -97,6 +100,11 @@ int hc_cluster_sum(const float* e, long n, int n_slices, int ev_cap, float pertu
   }
   if (overflow) return -1;
   if (pool.size() / kCTerms > 32767) return -1;
+  // the pending two-parity summaries (in the kernel: one thread per event, side by side)
+  for (int i = 0; i < total; ++i) {
+    ChunkEvent& r = events[i];
+    if (r.flags & (kEvTieLo | kEvTieHi)) resolve_tie_event(&r, &pool[(size_t)r.pool * kCTerms]);
+  }
   auto terms = [&](int slot, int j) { return pool[(size_t)slot * kCTerms + j]; };
   return walk_events(events.data(), first_event.data(), n_events.data(), n_slices, ev_cap, terms, sum) ? 1 : 0;
 }
