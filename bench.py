@@ -15,6 +15,10 @@ rows x V=128256 bf16 Zipf-shaped logits, temperature 0.7, top-p 0.95, per-row xo
              bandwidth of this pool (MEASURED_PEAKS.json) or the stated fallback
   cpu_baseline  the reference's own CPU sampler (compiled unmodified in oracle/_ref; the C
              restatement if that is absent) on this machine's host cores, N = 1 only
+  parity     after the timed region one more step is run from known RNG states and its ids are
+             compared with the CPU oracle (64 rows) and, for N > 1, with an all-gather of every
+             rank's own ids: a mismatch makes the run fail
+  other_configs  short device-timed runs of the other baseline shapes and modes (N = 1 only)
 
 --impl reference times the reference's CPU sampler alone on the same batch.
 """
@@ -37,10 +41,51 @@ WORKLOAD = "c3"
 NBUF = 4  # rotating input buffers: 4 x 65.7 MB > 126 MB of L2
 FALLBACK_HBM_GBS = 6650.0
 
-# DRAM bytes (read + write) of ONE launch of the sampling kernel on the benchmark batch, from
-# the ncu capture whose summary is kept under profiles/.
-NCU_DRAM_BYTES_GREEDY = 65_930_000  # 65.68 MB read + 0.25 MB written (mean of two captured launches)
-NCU_DRAM_BYTES_PER_LAUNCH = 67_100_000  # 65.9 MB read + 1.2 MB written (mean of two captured launches)
+PARITY_ROWS = 64
+KERNEL_SOURCES = ["executorch_b200/csrc/sampler_kernels.cu", "executorch_b200/csrc/guided_sum.cuh",
+                  "executorch_b200/csrc/cluster_topp.cuh", "executorch_b200/csrc/cluster_math.cuh",
+                  "executorch_b200/csrc/exact_math.cuh"]
+
+
+def kernel_source_hash():
+    """Hash of the kernel sources (git blob hashes, concatenated and hashed again)."""
+    import hashlib
+    h = hashlib.sha1()
+    for rel in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, rel), "rb") as f:
+            data = f.read()
+        h.update(hashlib.sha1(b"blob %d\0" % len(data) + data).hexdigest().encode())
+    return h.hexdigest()
+
+
+def dram_traffic(kernel: str):
+    """DRAM bytes (read + write) of one launch of `kernel` on the benchmark batch, from the ncu
+    capture recorded in profiles/traffic.json, and whether the kernel sources have changed since."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            t = json.load(f)
+        entry = t["kernels"][kernel]
+        return int(entry["dram_bytes_per_launch"]), t.get("source_hash") != kernel_source_hash()
+    except Exception:
+        return None, True
+
+
+def config_dict(gpus: int, greedy: bool, exchange: str):
+    """The `config` object; the same for both arms of the benchmark."""
+    from executorch_b200 import workloads as W
+    cfg = W.CONFIGS[WORKLOAD]
+    names = {"p2p": "ids stored into every peer's buffer by the kernel epilogue + symmetric-memory barrier on a "
+                    "side stream",
+             "p2p-in-kernel": "ids stored into every peer's buffer by the kernel epilogue + arrival marks and a "
+                              "bounded wait at the end of the same launch",
+             "nccl": "all_gather of int64 ids (NCCL)"}
+    return {
+        "workload": ("c3 second pass: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0 (argmax)" if greedy
+                     else "c3: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0.7, top-p 0.95, seed=row"),
+        "rows_per_gpu": cfg.rows, "vocab": cfg.vocab, "global_rows": cfg.rows * gpus,
+        "l2": f"{NBUF} rotating input batches ({NBUF * cfg.rows * cfg.vocab * 2 / 1e6:.0f} MB > 126 MB L2)",
+        "exchange": names[exchange] if gpus > 1 else "none",
+    }
 
 
 def hbm_peak():
@@ -98,15 +143,19 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_reference_pass(x_host, cfg, seeds, threads):
-    """One pass of the reference's CPU sampler over the batch. Returns (wall_s, kind, how)."""
+def cpu_reference_pass(x_host, cfg, seeds, threads, native=True):
+    """One pass of the reference's CPU sampler over the batch. Returns (wall_s, kind, how).
+    `native`: Sampler::sample<BFloat16> on the 16-bit logits (what sample_from_logits calls);
+    otherwise Sampler::sample<float> on their exact upcast (the parity oracle's own path)."""
     import oracle
     timing = {}
     if oracle.Reference.available(stable=False):
         ref = oracle.Reference(stable=False)
         ref.sample_rows(x_host, cfg.temperature, cfg.topp, seeds, dtype=cfg.dtype, threads=threads,
-                        native=True, timing=timing)
-        return timing["wall_seconds"], "reference", "Sampler::sample<BFloat16> of the unmodified sampler.cpp"
+                        native=native, timing=timing)
+        return timing["wall_seconds"], "reference", (
+            "Sampler::sample<BFloat16> of the unmodified sampler.cpp" if native
+            else "Sampler::sample<float> of the unmodified sampler.cpp on the upcast logits")
     r = oracle.Restatement()
     r.sample_rows(x_host, cfg.temperature, cfg.topp, seeds, dtype=cfg.dtype, threads=threads, timing=timing)
     return timing["wall_seconds"], "port", "C restatement (float on upcast logits)"
@@ -154,19 +203,81 @@ def run_reference(args, rank, world):
         w, kind, how = cpu_reference_pass(xs, cfg, ss, threads)
         t += w
     value = per_step * args.steps / t
+    # for the record: the same sampler on the fp32 upcast (the oracle's path), and on one thread
+    variants = {}
+    for label, nat, thr in (("float_upcast_all_threads", False, threads), ("native_one_thread", True, 1),
+                            ("float_upcast_one_thread", False, 1)):
+        n = max(min(per_step, 4 * thr), 1)
+        w, _, _ = cpu_reference_pass(x[:n], cfg, seeds[:n], thr, native=nat)
+        variants[label] = {"rows_per_s": n / w, "threads": thr, "rows": n}
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": "c3: 256 rows x V=128256 bf16 Zipf logits, T=0.7, top-p 0.95, seed=row",
-                   "rows": rows, "vocab": cfg.vocab, "rows_per_step": per_step},
+        "logits_dtype": "bf16", "data": "synthetic",
+        "config": config_dict(args.gpus, False, args.exchange),
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": kind,
-                         "sample": f"each step = {per_step} rows of the {rows}-row batch on {threads} threads; {how}"},
+                         "sample": f"each step = {per_step} rows of the {rows}-row batch on {threads} threads; {how}",
+                         "variants": variants},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def other_configs(dev, peak, kernel_choice):
+    """Short device-timed runs of the other baseline shapes and modes: mean launch time over a
+    few launches (CUDA events on the launching stream), logits bytes / time, fraction of the
+    HBM peak. Inputs rotate over buffers larger than L2 where the shape allows it."""
+    import numpy as np
+    import torch
+    from executorch_b200 import Sampler, seeds_to_states
+    from executorch_b200 import workloads as W
+
+    out = {}
+
+    def timed(name, rows, temperature, topp, label, reps=5, nbuf=2, single_calls=0):
+        cfg = W.CONFIGS[name]
+        bufs = [W.rows_torch(name, b * rows, rows, dev) for b in range(nbuf)]
+        s = Sampler(cfg.vocab, temperature, topp, 0, device=dev)
+        s.set_kernel_choice(kernel_choice)
+        seeds = np.arange(rows, dtype=np.uint64)
+        sts = [seeds_to_states(seeds, dev) for _ in range(reps + 2)]
+        for i in range(2):
+            s.sample_rows(bufs[i % nbuf], sts[i])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(reps):
+            s.sample_rows(bufs[i % nbuf], sts[2 + i])
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        nbytes = rows * cfg.vocab * W.BYTES[cfg.dtype]
+        rec = {"rows": rows, "vocab": cfg.vocab, "logits_dtype": cfg.dtype, "temperature": temperature, "topp": topp,
+               "kernel_ms": ms, "rows_per_s": rows / (ms * 1e-3), "gb_per_s": nbytes / (ms * 1e-3) / 1e9,
+               "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+        if single_calls:
+            # the reference-shaped call: one row, token back on the host, every draw
+            row = bufs[0][0]
+            s.sample(row)
+            t0 = time.perf_counter()
+            for _ in range(single_calls):
+                s.sample(row)
+            rec["us_per_draw_sample_call"] = (time.perf_counter() - t0) / single_calls * 1e6
+        s.close()
+        del bufs
+        torch.cuda.empty_cache()
+        out[label] = rec
+
+    timed("c1", 2048, 0.8, 0.9, "c1_topp_fp32_v32000")
+    timed("c1", 2048, 0.8, 1.0, "c1_multinomial_fp32_v32000")
+    timed("c2", 1, 0.7, 0.9, "c2_single_row_bf16_v128256", reps=50, nbuf=1, single_calls=50)
+    timed("c3", 256, 0.0, 0.95, "c3_greedy_bf16_v128256", reps=20, nbuf=4)
+    timed("c3", 256, 0.7, 1.0, "c3_multinomial_bf16_v128256", reps=10, nbuf=4)
+    timed("c4", 512, 1.0, 0.9, "c4_topp_fp16_v151936", reps=2, nbuf=1)
+    timed("c5", 2048, 0.8, 0.9, "c5_topp_bf16_v256000", reps=3, nbuf=1)
+    return out
 
 
 def main():
@@ -177,6 +288,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true")
+    ap.add_argument("--kernel", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="kernel choice of the handle (0 = automatic; see etb200_sampler_set_kernel_choice)")
     ap.add_argument("--greedy", action="store_true",
                     help="config 3's second pass instead of the headline: temperature 0 (argmax) on the same batch")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-in-kernel", "nccl"],
@@ -219,44 +333,56 @@ def main():
     local_ids = torch.empty(rows, dtype=torch.int64, device=dev)
     all_ids = torch.empty(total_rows, dtype=torch.int64, device=dev) if world > 1 else local_ids
     sampler = Sampler(vocab, 0.0 if args.greedy else cfg.temperature, cfg.topp, 0, device=dev)
+    sampler.set_kernel_choice(args.kernel)
     if args.greedy:
         args.no_cpu_baseline = True
 
-    exchange, exchange_name = None, "none"
-    if world > 1:
-        exchange_name = "all_gather of int64 ids (NCCL)"
-        if args.exchange in ("p2p", "p2p-in-kernel"):
-            try:
-                from executorch_b200.sharded import PeerIdExchange
-                exchange = PeerIdExchange(total_rows, dev)
-                exchange_name = ("ids stored into every peer's buffer by the kernel epilogue + "
-                                 + ("arrival marks and a bounded wait at the end of the same launch"
-                                    if args.exchange == "p2p-in-kernel" else "symmetric-memory barrier"))
-            except Exception as exc:  # symmetric memory unavailable: use the collective
-                exchange_name += f" (peer buffers unavailable: {type(exc).__name__})"
+    exchange, exchange_mode = None, (args.exchange if world > 1 else "none")
+    if world > 1 and args.exchange in ("p2p", "p2p-in-kernel"):
+        try:
+            from executorch_b200.sharded import PeerIdExchange
+            exchange = PeerIdExchange(total_rows, dev)
+        except Exception:  # symmetric memory unavailable: use the collective
+            exchange = None
         # every rank must take the same path
         flag = torch.tensor([1 if exchange is not None else 0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag) == 0:
-            exchange = None
+            exchange, exchange_mode = None, "nccl"
 
-    in_kernel_sync = args.exchange == "p2p-in-kernel"
+    in_kernel_sync = exchange_mode == "p2p-in-kernel"
 
-    def step(i):
+    def step(i, k_start=None, k_end=None):
+        """One step: sample this rank's rows and make every rank hold all ids. Returns the buffer
+        that will hold them (complete once the stream / the overlapped barrier has caught up)."""
+        if exchange is not None:
+            exchange.begin_step()
+        if k_start is not None:
+            k_start.record()
         if exchange is not None and in_kernel_sync:
             sampler.sample_rows_exchange(bufs[i % NBUF], states, exchange.dest_ptrs, exchange.mark_ptrs, rank,
                                          rank * rows, exchange.next_epoch())
-        elif exchange is not None:
+            if k_end is not None:
+                k_end.record()
+            return exchange.finish(barrier=False)
+        if exchange is not None:
             sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
-            exchange.finish()
-        else:
-            sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
-            if world > 1:
-                dist.all_gather_into_tensor(all_ids, local_ids)
+            if k_end is not None:
+                k_end.record()
+            # the barrier runs on a side stream: the next step's launch does not queue behind it
+            return exchange.finish(overlap=True)[0]
+        sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
+        if k_end is not None:
+            k_end.record()
+        if world > 1:
+            dist.all_gather_into_tensor(all_ids, local_ids)
+        return all_ids
 
     for i in range(warmup):
         states.copy_(states0)
         step(i)
+    if exchange is not None:
+        exchange.drain()
     torch.cuda.synchronize()
 
     # ---- device-timed region: K steps, inputs resident
@@ -273,20 +399,9 @@ def main():
     torch.cuda.synchronize()
     t0.record()
     for i in range(args.steps):
-        k_start[i].record()
-        if exchange is not None and in_kernel_sync:
-            sampler.sample_rows_exchange(bufs[i % NBUF], states, exchange.dest_ptrs, exchange.mark_ptrs, rank,
-                                         rank * rows, exchange.next_epoch())
-            k_end[i].record()
-        elif exchange is not None:
-            sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
-            k_end[i].record()
-            exchange.finish()
-        else:
-            sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
-            k_end[i].record()
-            if world > 1:
-                dist.all_gather_into_tensor(all_ids, local_ids)
+        step(i, k_start[i], k_end[i])
+    if exchange is not None:
+        exchange.drain()  # every step's exchange is complete inside the timed region
     t1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -302,6 +417,33 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         elapsed_ms, kernel_ms = float(tt[0]), float(tt[1])
     value = total_rows * args.steps / (elapsed_ms * 1e-3)
+
+    # ---- parity: one more step, from known states, checked outside the timed region
+    import oracle
+    vb = args.steps % NBUF
+    states.copy_(states0)
+    got_all = step(args.steps)
+    if exchange is not None:
+        exchange.drain()
+    torch.cuda.synchronize()
+    got_all = got_all.clone()
+    mine = got_all[rank * rows:(rank + 1) * rows] if world > 1 else got_all
+    exchange_verified = None
+    if world > 1:
+        # every rank's own ids of the same step, gathered by NCCL: the exchange must agree
+        ref_all = torch.empty(total_rows, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(ref_all, mine.contiguous())
+        okf = torch.tensor([1 if torch.equal(ref_all, got_all) else 0], device=dev)
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        exchange_verified = bool(int(okf))
+    parity_rows = parity_equal = 0
+    if rank == 0:
+        xh = bufs[vb][:PARITY_ROWS].cpu().view(torch.int16).numpy().view(np.uint16)
+        sd = seeds[:PARITY_ROWS]
+        want = oracle.Restatement().sample_rows(xh, 0.0 if args.greedy else cfg.temperature, cfg.topp, sd,
+                                                dtype=cfg.dtype, threads=min(16, os.cpu_count() or 1))
+        gh = mine[:PARITY_ROWS].cpu().numpy()
+        parity_rows, parity_equal = PARITY_ROWS, int((gh == want).sum())
 
     # ---- end to end through the host-buffer entry of the C ABI (pinned host logits)
     host_bufs = [b.cpu().view(torch.int16).pin_memory().view(torch.bfloat16) for b in bufs[:2]]
@@ -329,23 +471,21 @@ def main():
         peak, which = hbm_peak()
         algo_bytes = rows * (vocab * 2 + 8 + 16)  # logits once + id + rng state in/out
         achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        kernel_name = "argmax_rows_kernel" if args.greedy else "sample_rows_kernel"
+        traffic, stale = dram_traffic(kernel_name)
         line = {
             "metric": "argmax_rows_per_s_v128256_bf16" if args.greedy else METRIC,
             "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {
-                "workload": ("c3 second pass: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0 (argmax)" if args.greedy
-                             else "c3: 256 rows x V=128256 bf16 Zipf logits per GPU, T=0.7, top-p 0.95, seed=row"),
-                "rows_per_gpu": rows, "vocab": vocab, "global_rows": total_rows,
-                "l2": f"{NBUF} rotating input batches ({NBUF * rows * vocab * 2 / 1e6:.0f} MB > 126 MB L2)",
-                "exchange": exchange_name,
-            },
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "logits_dtype": "bf16",
+            "data": "synthetic",
+            "config": config_dict(world, args.greedy, exchange_mode if world > 1 else args.exchange),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak,
-                         "traffic": NCU_DRAM_BYTES_GREEDY if args.greedy else NCU_DRAM_BYTES_PER_LAUNCH,
-                         "peak_source": f"of {which}", "kernel_ms": kernel_ms,
+                         "frac": achieved / peak, "traffic": traffic, "traffic_stale": stale,
+                         "peak_source": f"of {which}", "kernel_ms": kernel_ms, "kernel": kernel_name,
                          "algorithmic_bytes_per_launch": algo_bytes},
+            "parity": {"checked_rows": parity_rows, "equal": parity_equal, "exchange_verified": exchange_verified,
+                       "against": "CPU oracle (C restatement of sampler.cpp) on the rows of one extra step"},
             "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / args.e2e_steps},
             "gpu_launches": int(launches),
@@ -354,10 +494,18 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             x_host = host_bufs[0].view(torch.int16).numpy().view(np.uint16)
             line["cpu_baseline"] = cpu_baseline(x_host, cfg, seeds)
+        if world == 1 and not args.no_other_configs and not args.greedy:
+            del bufs, host_bufs
+            torch.cuda.empty_cache()
+            line["other_configs"] = other_configs(dev, peak, args.kernel)
         print(json.dumps(line), flush=True)
     sampler.close()
     if world > 1:
         dist.destroy_process_group()
+    if parity_rows and parity_equal != parity_rows:
+        raise SystemExit(f"parity check failed: {parity_equal} of {parity_rows} rows equal the oracle's tokens")
+    if exchange_verified is False:
+        raise SystemExit("the id exchange did not leave every rank with every rank's ids")
 
 
 if __name__ == "__main__":
