@@ -28,6 +28,7 @@ SYMBOLS = {
                                                    C.POINTER(C.c_void_p)]),
     "etb200_sampler_destroy": (C.c_uint32, [C.c_void_p]),
     "etb200_sampler_set_temperature": (C.c_uint32, [C.c_void_p, C.c_float]),
+    "etb200_sampler_set_inv_temperature": (C.c_uint32, [C.c_void_p, C.c_float]),
     "etb200_sampler_set_topk": (C.c_uint32, [C.c_void_p, C.c_int32]),
     "etb200_sampler_get_rng_state": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "etb200_sampler_set_rng_state": (C.c_uint32, [C.c_void_p, C.c_uint64]),

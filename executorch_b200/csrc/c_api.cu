@@ -128,6 +128,10 @@ etb200_error_t create_impl(
     return fail(ETB200_INTERNAL, "no CUDA device available (%s); this library has no CPU path",
                 e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
   }
+  if (device == -1) {  // the calling thread's current device
+    e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(ETB200_INTERNAL, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  }
   ETB_CHECK_ARG(device >= 0 && device < ndev, "device %d out of range [0, %d)", device, ndev);
   DeviceGuard guard(device);
   if (guard.err != cudaSuccess)
@@ -375,6 +379,12 @@ etb200_error_t etb200_sampler_set_temperature(etb200_sampler_t* h, float tempera
   ETB_CHECK_ARG(h != nullptr, "handle is null");
   if (temperature < 0.0f) temperature = 0.0f;
   h->inv_temperature = inv_temperature_of(temperature);
+  return ETB200_OK;
+}
+
+etb200_error_t etb200_sampler_set_inv_temperature(etb200_sampler_t* h, float inv_temperature) {
+  ETB_CHECK_ARG(h != nullptr, "handle is null");
+  h->inv_temperature = inv_temperature;
   return ETB200_OK;
 }
 

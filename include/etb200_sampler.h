@@ -67,7 +67,7 @@ typedef struct etb200_sampler etb200_sampler_t;
 /* Sampler::Sampler(vocab_size, temperature, topp, rng_seed), sampler.cpp:173-181.
  * temperature 0 selects greedy argmax; it is not clamped here (a negative value keeps
  * 1/temperature, as in the reference). `device` is the CUDA device ordinal that owns the
- * handle's state and scratch memory. */
+ * handle's state and scratch memory; -1 means the calling thread's current device. */
 ETB200_EXPORT etb200_error_t etb200_sampler_create(
     int32_t vocab_size, float temperature, float topp, uint64_t rng_seed, int32_t device,
     etb200_sampler_t** out_handle);
@@ -83,6 +83,11 @@ ETB200_EXPORT etb200_error_t etb200_sampler_destroy(etb200_sampler_t* handle);
 /* Sampler::set_temperature, sampler.h:48-53: negative values are reset to 0. */
 ETB200_EXPORT etb200_error_t etb200_sampler_set_temperature(
     etb200_sampler_t* handle, float temperature);
+
+/* Sets Sampler::inv_temperature_ (sampler.h:78) directly: for a binding that keeps the
+ * reference's own member and must hand its exact value on (1 / (1 / T) is not always T). */
+ETB200_EXPORT etb200_error_t etb200_sampler_set_inv_temperature(
+    etb200_sampler_t* handle, float inv_temperature);
 
 /* Sampler::set_topk, sampler.h:58-60. k <= 0 or k >= vocab_size disables top-k; an active
  * top-k takes precedence over top-p (sampler.cpp:239-241). */
