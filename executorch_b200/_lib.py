@@ -21,6 +21,13 @@ MEMORY_ALLOCATION_FAILED = 0x21
 DTYPE_HALF, DTYPE_FLOAT, DTYPE_BFLOAT16, DTYPE_UINT16 = 5, 6, 15, 27
 
 # every symbol include/etb200_sampler.h declares: (restype, argtypes)
+class RowOptions(C.Structure):
+    """etb200_row_options_t of include/etb200_sampler.h."""
+    _fields_ = [("temperature_device", C.c_void_p), ("topp_device", C.c_void_p), ("topk_device", C.c_void_p),
+                ("scale", C.c_float), ("edit_offsets_device", C.c_void_p), ("edit_ids_device", C.c_void_p),
+                ("edit_bias_device", C.c_void_p), ("n_edits", C.c_int64)]
+
+
 SYMBOLS = {
     "etb200_sampler_create": (C.c_uint32, [C.c_int32, C.c_float, C.c_float, C.c_uint64, C.c_int32,
                                            C.POINTER(C.c_void_p)]),
@@ -36,6 +43,8 @@ SYMBOLS = {
                                            C.POINTER(C.c_int32)]),
     "etb200_sampler_sample_rows": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
                                                 C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "etb200_sampler_sample_rows_ex": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
+                                                   C.c_void_p, C.c_void_p, C.POINTER(RowOptions), C.c_void_p]),
     "etb200_sampler_sample_rows_scatter": (C.c_uint32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
                                                         C.c_int64, C.c_void_p, C.POINTER(C.c_void_p),
                                                         C.c_int32, C.c_int64, C.c_void_p]),

@@ -464,6 +464,52 @@ etb200_error_t etb200_sampler_sample_rows(
       static_cast<cudaStream_t>(stream));
 }
 
+etb200_error_t etb200_sampler_sample_rows_ex(
+    etb200_sampler_t* h, void* logits_device, int32_t dtype, int64_t rows, int64_t row_stride_elems,
+    uint64_t* rng_states_device, int64_t* out_ids_device, const etb200_row_options_t* opt, void* stream) {
+  etb200_error_t err = check_common(h, logits_device, dtype, rows, row_stride_elems, out_ids_device);
+  if (err != ETB200_OK) return err;
+  if (rows == 0) return ETB200_OK;
+  etb200_row_options_t none = {};
+  none.scale = 1.0f;
+  if (opt == nullptr) opt = &none;
+  ETB_CHECK_ARG(opt->scale > 0.0f && opt->scale < 3.0e38f, "scale must be a positive finite number, got %g",
+                (double)opt->scale);
+  ETB_CHECK_ARG(opt->n_edits >= 0, "n_edits must be >= 0");
+  ETB_CHECK_ARG(opt->n_edits == 0 || (opt->edit_ids_device != nullptr && opt->edit_bias_device != nullptr),
+                "edit_ids_device / edit_bias_device are null but n_edits is %lld", (long long)opt->n_edits);
+  ETB_CHECK_ARG(opt->n_edits == 0 || row_stride_elems >= h->vocab || rows == 1,
+                "edits need rows that do not share memory (row_stride_elems >= vocab_size)");
+  if (dtype == kDtypeUInt16)
+    return fail(ETB200_NOT_SUPPORTED, "UInt16 logits are raw integers: only etb200_sampler_sample_rows at temperature 0");
+  DeviceGuard guard(h->device);
+  unsigned long long* states = reinterpret_cast<unsigned long long*>(rng_states_device);
+  const bool all_greedy = h->inv_temperature == 0.0f && opt->temperature_device == nullptr;
+  if (states == nullptr && !all_greedy) {
+    ETB_CHECK_ARG(rows == 1, "rng_states may be NULL only for a single row (rows = %lld)", (long long)rows);
+    states = h->d_state;
+  }
+  const int blocks = grid_blocks(h, dtype, rows);
+  err = ensure_scratch(h, blocks);  // a row may use top-p or top-k whatever the handle says
+  if (err != ETB200_OK) return err;
+  RowSettings rs;
+  rs.temperature = opt->temperature_device;
+  rs.topp = opt->topp_device;
+  rs.topk = opt->topk_device;
+  rs.scale = opt->scale;
+  RowEdits ed;
+  ed.offsets = reinterpret_cast<const long long*>(opt->edit_offsets_device);
+  ed.ids = opt->n_edits > 0 ? opt->edit_ids_device : nullptr;
+  ed.bias = opt->edit_bias_device;
+  ed.n_shared = opt->n_edits;
+  const int topk = (h->topk > 0 && h->topk < h->vocab) ? h->topk : 0;
+  ETB_CUDA(launch_sample_rows_ext(dtype, logits_device, rows, h->vocab, row_stride_elems, h->inv_temperature,
+                                  h->topp, topk, rs, ed, states, out_ids_device, h->scratch, blocks, h->table,
+                                  h->d_status, static_cast<cudaStream_t>(stream)));
+  h->launches += opt->n_edits > 0 ? 2 : 1;
+  return ETB200_OK;
+}
+
 etb200_error_t etb200_sampler_sample_rows_scatter(
     etb200_sampler_t* h, const void* logits_device, int32_t dtype, int64_t rows,
     int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* const* dest_buffers,

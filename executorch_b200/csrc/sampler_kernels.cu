@@ -100,10 +100,11 @@ struct GuidedShared {
 struct NoGuidedShared {};
 static_assert(kGEventCap <= kThreads, "one thread per event resolves the pending summaries");
 
-template <bool kLut, bool kGuided = false>
+template <bool kLut, bool kGuided = false, bool kExtended = false>
 struct __align__(16) Shared {
   // (members read with vector loads carry their own alignas)
   static constexpr bool kHasLut = kLut;
+  static constexpr bool kExt = kExtended;  // per-row settings and the fused scalar multiply
   typename std::conditional<kGuided, GuidedShared, NoGuidedShared>::type g;
   uint64_t exp_tab[kExpTableSize];
   float lut[kLut ? kLutSize : 2];
@@ -714,9 +715,23 @@ struct RowMath {
   float mx;
   float sum;   // divisor when probs is set
   bool probs;
+  float scale = 1.0f;  // extended entry point only: every logit is first multiplied by this, in T
+
+  // The logit as the sampler sees it: a "multiply" logit processor folded into the load
+  // (logit_processor.h:34-40 works in place on T, so the product is rounded to T).
+  __device__ __forceinline__ float xform(float logit) const {
+    if constexpr (S::kExt) {
+      const float y = __fmul_rn(logit, scale);
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) return __bfloat162float(__float2bfloat16_rn(y));
+      if constexpr (std::is_same<T, __half>::value) return __half2float(__float2half_rn(y));
+      return y;
+    } else {
+      return logit;
+    }
+  }
 
   __device__ __forceinline__ float direct(float logit, const S& sm) const {
-    const float e = expf_ref(__fsub_rn(__fmul_rn(logit, inv_t), mx), sm.exp_tab);
+    const float e = expf_ref(__fsub_rn(__fmul_rn(xform(logit), inv_t), mx), sm.exp_tab);
     return probs ? __fdiv_rn(e, sum) : e;
   }
 
@@ -849,7 +864,7 @@ __device__ __forceinline__ __nv_bfloat162 neg_inf2(__nv_bfloat16) {
 // Max over the row of logit * inv_t (softmax, sampler.cpp:191-196).
 template <typename T, typename S>
 __device__ __forceinline__ float row_max_scaled(
-    S& sm, const T* __restrict__ row, int vocab, bool vec_ok, float inv_t) {
+    S& sm, const RowMath<T, S>& rm, const T* __restrict__ row, int vocab, bool vec_ok, float inv_t) {
   const int tid = threadIdx.x;
   if constexpr (sizeof(T) == 2) {
     if (inv_t > 0.0f) {
@@ -878,11 +893,11 @@ __device__ __forceinline__ float row_max_scaled(
       float m = fmaxf(to_f32(acc.x), to_f32(acc.y));
       for (int i = nvec * 8 + tid; i < vocab; i += kThreads) m = fmaxf(m, to_f32(row[i]));
       m = block_max(sm, m);
-      return __fmul_rn(m, inv_t);
+      return __fmul_rn(rm.xform(m), inv_t);  // the multiply is by a positive factor: monotone too
     }
   }
   float mx = -INFINITY;
-  for (int i = tid; i < vocab; i += kThreads) mx = fmaxf(mx, __fmul_rn(to_f32(row[i]), inv_t));
+  for (int i = tid; i < vocab; i += kThreads) mx = fmaxf(mx, __fmul_rn(rm.xform(to_f32(row[i])), inv_t));
   return block_max(sm, mx);
 }
 
@@ -1375,20 +1390,68 @@ __device__ bool small_tail(
   return true;
 }
 
+// Greedy choice for one row inside the sampling kernel (extended entry point): strict '>' in
+// index order on the values the sampler sees, as sample_argmax (sampler.cpp:44-56) -- the
+// lowest index among equal maxima, a NaN never replaces the running maximum, a NaN in
+// element 0 is never replaced. Block-uniform result.
+template <typename T, typename S>
+__device__ int block_argmax(S& sm, const RowMath<T, S>& rm, int vocab) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int i = tid; i < vocab; i += kThreads) {
+    const float x = rm.xform(to_f32(rm.row[i]));
+    if (x > best) {
+      best = x;
+      besti = i;
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, d);
+    if (ov > best || (ov == best && oi < besti)) {
+      best = ov;
+      besti = oi;
+    }
+  }
+  __syncthreads();
+  if (lane == 0) {
+    sm.redf[warp] = best;
+    sm.redi[warp] = besti;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < kWarps; ++w) {
+      if (sm.redf[w] > best || (sm.redf[w] == best && sm.redi[w] < besti)) {
+        best = sm.redf[w];
+        besti = sm.redi[w];
+      }
+    }
+    const float first = rm.xform(to_f32(rm.row[0]));
+    sm.misc_i[0] = (first != first || besti == 0x7fffffff) ? 0 : besti;
+  }
+  __syncthreads();
+  const int token = sm.misc_i[0];
+  __syncthreads();
+  return token;
+}
+
 #include "guided_sum.cuh"
 
 // ---------------------------------------------------------------------------------------
 // The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
 // otherwise. Follows Sampler::sample<float> (sampler.cpp:222-251).
 // ---------------------------------------------------------------------------------------
-template <typename T, bool kLut, bool kGuided>
+template <typename T, bool kLut, bool kGuided, bool kExt = false>
 __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
-    const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t,
-    float topp, int topk, unsigned long long* __restrict__ rng_states,
+    const T* __restrict__ logits, int64_t rows, int vocab, int64_t row_stride, float inv_t0,
+    float topp0, int topk0, unsigned long long* __restrict__ rng_states,
     int64_t* __restrict__ out_ids, PeerOut peers, Entry* scratch, ExpTable table,
     int* __restrict__ status, const int* __restrict__ row_list, const int* __restrict__ row_count,
-    int* __restrict__ retry_rows, int* __restrict__ retry_count, int* __restrict__ retry_count_next) {
-  using S = Shared<kLut, kGuided>;
+    int* __restrict__ retry_rows, int* __restrict__ retry_count, int* __restrict__ retry_count_next,
+    RowSettings ext) {
+  using S = Shared<kLut, kGuided, kExt>;
   // the block's shared state exceeds the 48 KB static limit: dynamic shared memory, sized
   // sizeof(S) by the launcher
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -1410,10 +1473,6 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     }
   }
   __syncthreads();
-  // mode selection of Sampler::sample (sampler.cpp:239-248): top-k wins over top-p
-  const bool use_topk = topk > 0 && topk < vocab;
-  const bool use_topp = !use_topk && !(topp <= 0.0f || topp >= 1.0f);
-  const bool use_list = use_topk || use_topp;  // modes that collect candidates during pass 2
   Entry* listA = scratch + (size_t)blockIdx.x * 2 * (size_t)vocab;
   Entry* listB = listA + vocab;
 
@@ -1421,6 +1480,22 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   const int64_t n_todo = row_list != nullptr ? (int64_t)*row_count : rows;
   for (int64_t it = blockIdx.x; it < n_todo; it += gridDim.x) {
     const int64_t r = row_list != nullptr ? (int64_t)row_list[it] : it;
+    // the row's settings: the handle's, or -- extended entry point -- its own
+    // (LLMSession's SamplingConfig{temperature, top_p, top_k, seed}, llm_session.h:29-34)
+    float inv_t = inv_t0, topp = topp0;
+    int topk = topk0;
+    if constexpr (kExt) {
+      if (ext.temperature != nullptr) {
+        const float t = ext.temperature[r];
+        inv_t = t > 0.0f ? 1.0f / t : 0.0f;  // as Sampler::set_temperature: negative counts as 0
+      }
+      if (ext.topp != nullptr) topp = ext.topp[r];
+      if (ext.topk != nullptr) topk = ext.topk[r];
+    }
+    // mode selection of Sampler::sample (sampler.cpp:239-248): top-k wins over top-p
+    const bool use_topk = topk > 0 && topk < vocab;
+    const bool use_topp = !use_topk && !(topp <= 0.0f || topp >= 1.0f);
+    const bool use_list = use_topk || use_topp;  // modes that collect candidates during pass 2
     RowMath<T, S> rm;
     rm.row = logits + r * row_stride;
     rm.vocab = vocab;
@@ -1428,10 +1503,20 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     rm.inv_t = inv_t;
     rm.sum = 1.0f;
     rm.probs = false;
+    if constexpr (kExt) {
+      rm.scale = ext.scale;
+      if (inv_t == 0.0f) {
+        // a greedy row among sampled ones (sampler.cpp:226-228): no coin, the state stays
+        const int token = block_argmax(sm, rm, vocab);
+        store_token(out_ids, peers, r, token);
+        __syncthreads();
+        continue;
+      }
+    }
 
     ETB_STAMP(0);
     // ---- pass 1: max of the scaled logits
-    rm.mx = row_max_scaled<T>(sm, rm.row, vocab, rm.vec_ok, inv_t);
+    rm.mx = row_max_scaled<T>(sm, rm, rm.row, vocab, rm.vec_ok, inv_t);
 
     // the coin is drawn once per sampled row (sampler.cpp:237); the guided variant stores the
     // advanced state only once it knows that it decides the row
@@ -1903,7 +1988,8 @@ static cudaError_t launch_sample_t(
   sample_rows_kernel<T, kLut, false><<<blocks, kThreads, sizeof(Shared<kLut>), stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       peers,
-      static_cast<Entry*>(scratch), table, status, row_list, row_count, nullptr, nullptr, nullptr);
+      static_cast<Entry*>(scratch), table, status, row_list, row_count, nullptr, nullptr, nullptr,
+      RowSettings{nullptr, nullptr, nullptr, 1.0f});
   return cudaGetLastError();
 }
 
@@ -1918,7 +2004,7 @@ static cudaError_t launch_guided_t(
   sample_rows_kernel<T, kLut, true><<<blocks, kThreads, sizeof(Shared<kLut, true>), stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       peers, static_cast<Entry*>(scratch), table, status, nullptr, nullptr, retry_rows, retry_count,
-      retry_count_next);
+      retry_count_next, RowSettings{nullptr, nullptr, nullptr, 1.0f});
   return cudaGetLastError();
 }
 
@@ -1940,6 +2026,89 @@ cudaError_t launch_sample_rows(
       return launch_sample_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp, topk,
                                                   rng_states, out_ids, peers, scratch, blocks, table,
                                                   status, row_list, row_count, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
+namespace {
+
+// One thread per edit: logits[row][id] = T(float(logits[row][id]) + bias), what a mask or bias
+// logit processor does in place (logit_processor.h:34-40).
+template <typename T>
+__global__ void apply_row_edits_kernel(T* logits, int64_t rows, int vocab, int64_t row_stride, RowEdits ed,
+                                       long long total) {
+  const long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (j >= total) return;
+  int64_t row;
+  long long e;
+  if (ed.offsets == nullptr) {
+    row = j / ed.n_shared;
+    e = j % ed.n_shared;
+  } else {
+    // the row that owns entry j: the last row whose first entry is not behind j
+    int64_t lo = 0, hi = rows - 1;
+    while (lo < hi) {
+      const int64_t mid = (lo + hi + 1) / 2;
+      if (ed.offsets[mid] <= j) lo = mid; else hi = mid - 1;
+    }
+    row = lo;
+    e = j;
+  }
+  const int id = ed.ids[e];
+  if (id < 0 || id >= vocab) return;  // out of range: no-op, as the reference's processors
+  T* p = logits + row * row_stride + id;
+  const float v = to_f32(*p) + ed.bias[e];
+  if constexpr (std::is_same<T, float>::value) {
+    *p = v;
+  } else if constexpr (std::is_same<T, __half>::value) {
+    *p = __float2half_rn(v);
+  } else {
+    *p = __float2bfloat16_rn(v);
+  }
+}
+
+template <typename T, bool kLut>
+cudaError_t launch_ext_t(
+    void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp, int topk,
+    const RowSettings& settings, const RowEdits& edits, long long n_edits, unsigned long long* rng_states,
+    int64_t* out_ids, void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
+  if (n_edits > 0) {
+    const long long grid = (n_edits + 255) / 256;
+    apply_row_edits_kernel<T><<<(unsigned)grid, 256, 0, stream>>>(static_cast<T*>(logits), rows, vocab, row_stride,
+                                                                  edits, n_edits);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  cudaError_t attr = cudaFuncSetAttribute(sample_rows_kernel<T, kLut, false, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)sizeof(Shared<kLut, false, true>));
+  if (attr != cudaSuccess) return attr;
+  sample_rows_kernel<T, kLut, false, true><<<blocks, kThreads, sizeof(Shared<kLut, false, true>), stream>>>(
+      static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids, PeerOut{},
+      static_cast<Entry*>(scratch), table, status, nullptr, nullptr, nullptr, nullptr, nullptr, settings);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_sample_rows_ext(
+    int dtype, void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
+    int topk, const RowSettings& settings, const RowEdits& edits, unsigned long long* rng_states,
+    int64_t* out_ids, void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream) {
+  // how many edits there are is known on the host: shared lists directly, per-row lists by
+  // their last offset, which the caller passes in n_shared as well
+  const long long n_edits = edits.ids == nullptr ? 0 : (edits.offsets == nullptr ? edits.n_shared * rows : edits.n_shared);
+  switch (dtype) {
+    case kDtypeFloat:
+      return launch_ext_t<float, false>(logits, rows, vocab, row_stride, inv_t, topp, topk, settings, edits,
+                                        n_edits, rng_states, out_ids, scratch, blocks, table, status, stream);
+    case kDtypeHalf:
+      return launch_ext_t<__half, false>(logits, rows, vocab, row_stride, inv_t, topp, topk, settings, edits,
+                                         n_edits, rng_states, out_ids, scratch, blocks, table, status, stream);
+    case kDtypeBFloat16:
+      return launch_ext_t<__nv_bfloat16, true>(logits, rows, vocab, row_stride, inv_t, topp, topk, settings, edits,
+                                               n_edits, rng_states, out_ids, scratch, blocks, table, status, stream);
     default:
       return cudaErrorInvalidValue;
   }

@@ -37,6 +37,27 @@ struct PeerOut {
   unsigned long long wait_ns;  // limit of that wait, in nanoseconds of the GPU's global timer
 };
 
+// Per-row settings of the extended entry point (device arrays of `rows` entries, or null for
+// "the handle's value"), and the scalar that multiplies every logit (1 = none).
+struct RowSettings {
+  const float* temperature;
+  const float* topp;
+  const int* topk;
+  float scale;
+};
+
+// Sparse in-place edits of the logits before sampling (mask / bias logit processors): entry j
+// adds bias[j] to logit ids[j] of its row (-inf masks the token; ids outside [0, vocab) are
+// ignored). Row r owns entries [offsets[r], offsets[r + 1]) and n_shared is the total number of
+// entries; with offsets == null the n_shared entries apply to every row. All pointers are
+// device pointers; ids == null means "no edits".
+struct RowEdits {
+  const long long* offsets;
+  const int* ids;
+  const float* bias;
+  long long n_shared;
+};
+
 // Bytes of candidate-list scratch the sampling kernel needs when launched with `blocks`
 // thread blocks on rows of `vocab` logits.
 size_t sampler_scratch_bytes(int vocab, int blocks);
@@ -84,6 +105,14 @@ cudaError_t launch_topp_cluster(
     unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, const ExpTable& table,
     void* scratch, int64_t batch_rows, int* retry_rows, int* retry_count, int* retry_count_next,
     cudaStream_t stream);
+
+// The extended form of launch_sample_rows: first the edits are applied to the logits in
+// place (one thread per edit), then every row is sampled with its own settings; a row whose
+// temperature is 0 takes the argmax. `logits` is written only at the edited positions.
+cudaError_t launch_sample_rows_ext(
+    int dtype, void* logits, int64_t rows, int vocab, int64_t row_stride, float inv_t, float topp,
+    int topk, const RowSettings& settings, const RowEdits& edits, unsigned long long* rng_states,
+    int64_t* out_ids, void* scratch, int blocks, const ExpTable& table, int* status, cudaStream_t stream);
 
 // temperature == 0: greedy argmax of every row.
 cudaError_t launch_argmax_rows(

@@ -157,6 +157,51 @@ class Sampler:
             states_ptr, C.c_void_p(out.data_ptr()), self._stream()))
         return out
 
+    def sample_rows_ex(self, logits: torch.Tensor, rng_states: torch.Tensor | None, *,
+                       temperature: torch.Tensor | None = None, topp: torch.Tensor | None = None,
+                       topk: torch.Tensor | None = None, scale: float = 1.0,
+                       edit_ids: torch.Tensor | None = None, edit_bias: torch.Tensor | None = None,
+                       edit_offsets: torch.Tensor | None = None,
+                       out: torch.Tensor | None = None) -> torch.Tensor:
+        """``sample_rows`` for a serving batch: per-row ``temperature`` / ``topp`` (float32) and
+        ``topk`` (int32) device tensors replace the handle's settings (``SamplingConfig`` of
+        ``LLMSession::decode_one``); ``edit_ids`` (int32) / ``edit_bias`` (float32, -inf masks)
+        are added to the logits IN PLACE first -- for every row, or for the rows that
+        ``edit_offsets`` (int64, rows + 1 entries) assigns them to -- and ``scale`` multiplies
+        every logit as the kernel reads it: the mask, bias and multiply logit processors."""
+        self._check_rows(logits)
+        rows = logits.shape[0]
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int64, device=self.device)
+        opt = _lib.RowOptions()
+        opt.scale = float(scale)
+
+        def ptr(t, dtype, n, name):
+            if t is None:
+                return None
+            if t.dtype != dtype or t.numel() != n or not t.is_contiguous() or t.device != self.device:
+                raise ValueError(f"{name} must be a contiguous {dtype} device tensor with {n} entries")
+            return t.data_ptr()
+
+        opt.temperature_device = ptr(temperature, torch.float32, rows, "temperature")
+        opt.topp_device = ptr(topp, torch.float32, rows, "topp")
+        opt.topk_device = ptr(topk, torch.int32, rows, "topk")
+        n_edits = 0 if edit_ids is None else edit_ids.numel()
+        opt.n_edits = n_edits
+        opt.edit_ids_device = ptr(edit_ids, torch.int32, n_edits, "edit_ids")
+        opt.edit_bias_device = ptr(edit_bias, torch.float32, n_edits, "edit_bias")
+        opt.edit_offsets_device = ptr(edit_offsets, torch.int64, rows + 1, "edit_offsets")
+        states_ptr = C.c_void_p(0)
+        if rng_states is not None:
+            if (rng_states.dtype != torch.int64 or rng_states.numel() != rows
+                    or not rng_states.is_contiguous() or rng_states.device != self.device):
+                raise ValueError("rng_states must be a contiguous int64 device tensor, one per row")
+            states_ptr = C.c_void_p(rng_states.data_ptr())
+        _lib.check(_lib.load().etb200_sampler_sample_rows_ex(
+            self._h, C.c_void_p(logits.data_ptr()), _dtype_code(logits), rows, logits.stride(0),
+            states_ptr, C.c_void_p(out.data_ptr()), C.byref(opt), self._stream()))
+        return out
+
     def sample_rows_scatter(self, logits: torch.Tensor, rng_states: torch.Tensor | None,
                             dest_ptrs, dest_offset: int) -> None:
         """Like ``sample_rows``, but the id of row r is stored into every int64 buffer of

@@ -122,6 +122,41 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows(
     int64_t row_stride_elems, uint64_t* rng_states_device, int64_t* out_ids_device,
     void* stream);
 
+/* Per-row settings and logit edits for etb200_sampler_sample_rows_ex. Every pointer is a device
+ * pointer and may be NULL ("not used"). */
+typedef struct {
+  /* SamplingConfig{temperature, top_p, top_k} per request (extension/llm/runner/llm_session.h:
+   * 29-34; the seed is the row's RNG state): arrays of `rows` entries that replace the handle's
+   * setting for each row. A temperature <= 0 makes that row greedy (its state is not advanced);
+   * top_k outside (0, vocab_size) means "no top-k"; top_p outside (0, 1) means multinomial. */
+  const float* temperature_device;
+  const float* topp_device;
+  const int32_t* topk_device;
+  /* A "multiply" logit processor (logit_processor.h:34-40) folded into the kernel's reads: every
+   * logit is seen as T(logit * scale), T the logits' dtype. Must be > 0; 1 = none. */
+  float scale;
+  /* Mask / bias logit processors: entry j adds edit_bias[j] to logit edit_ids[j] of its row, in
+   * place, rounded to the logits' dtype (-inf masks the token; ids outside [0, vocab_size) are
+   * ignored, as the reference's processors ignore them). With edit_offsets (rows + 1 entries,
+   * ascending, edit_offsets[rows] == n_edits) row r owns entries [edit_offsets[r],
+   * edit_offsets[r + 1]); without, all n_edits entries apply to every row. Edits are applied
+   * before the multiply, and before sampling; only the edited logits are written. */
+  const int64_t* edit_offsets_device;
+  const int32_t* edit_ids_device;
+  const float* edit_bias_device;
+  int64_t n_edits;
+} etb200_row_options_t;
+
+/* etb200_sampler_sample_rows for a serving batch whose rows carry their own settings, with the
+ * usual logit processors applied on the device: what apply_logit_processors + logits_to_token do
+ * per request in the decode loop (extension/llm/runner/text_token_generator.h:143-148), for all
+ * rows in one launch (two when there are edits: they are scattered into the logits first, one
+ * thread per edit, so no processor costs a pass over the logits). `logits_device` is therefore
+ * not const; `options` may be NULL. No multi-GPU form. */
+ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_ex(
+    etb200_sampler_t* handle, void* logits_device, int32_t dtype, int64_t rows, int64_t row_stride_elems,
+    uint64_t* rng_states_device, int64_t* out_ids_device, const etb200_row_options_t* options, void* stream);
+
 /* Multi-GPU form of etb200_sampler_sample_rows (no counterpart in the reference, which is
  * single-device): instead of one out_ids array, the kernel's epilogue stores the id of row r
  * into EVERY buffer dest_buffers[0..n_dest) at index dest_offset + r. The buffers are int64
