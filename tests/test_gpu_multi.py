@@ -39,10 +39,24 @@ def _worker(rank, world, port, q):
                                 in_kernel_sync=mode == "p2p-in-kernel")
             lo, n = sh.start, sh.count
             t = torch.from_numpy(x[lo:lo + n].view(np.int16)).to(dev).view(torch.bfloat16)
-            for _ in range(3):  # repeated steps reuse the exchange buffer
-                ids = sh.sample_rows(t, seeds_to_states(seeds[lo:lo + n], dev))
+            kept = []
+            for k in range(4):
+                # every step draws from other seeds, so a buffer that a faster rank overwrote
+                # with its next step's ids would hold wrong tokens
+                sk = seeds + np.uint64(1000 * k)
+                wk = want if k == 0 else oracle.Restatement().sample_rows(x, 0.7, 0.9, sk, dtype="bf16", threads=2)
+                ids = sh.sample_rows(t, seeds_to_states(sk[lo:lo + n], dev))
+                if rank == world - 1 and mode != "nccl":
+                    torch.cuda._sleep(20_000_000)  # a slow consumer: this rank reads its ids late
+                kept.append((ids, wk))
+                if mode != "nccl" and len(kept) == 2:
+                    # the previous step's ids are still intact while the next step is in flight
+                    # (the exchange rotates over three regions)
+                    torch.cuda.synchronize()
+                    ok = ok and np.array_equal(kept[0][0].cpu().numpy(), kept[0][1])
+                    kept.pop(0)
                 torch.cuda.synchronize()
-                ok = ok and np.array_equal(ids.cpu().numpy(), want)
+                ok = ok and np.array_equal(ids.cpu().numpy(), wk)
             dist.barrier()
         ok = ok and s.status == 0  # no arrival wait ran out
         s.close()
