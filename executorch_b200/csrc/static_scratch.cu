@@ -36,6 +36,9 @@ constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 void* g_scratch_ptr[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
+int g_blocks_per_sm[kMaxDevices][3] = {};  // occupancy of the sampling kernel per dtype, queried once
+bool g_table_ready = false;
+ExpTable g_table;  // host-side constants of the kernels' exponential, built once per process
 
 thread_local char g_static_err[256] = "";
 
@@ -58,16 +61,33 @@ etb200_error_t setup_current_device(int* device_out, void** ptr_out, int* sm_cou
       return fail(ETB200_INTERNAL, e != cudaSuccess ? cudaGetErrorString(e)
                                                    : "cudaGetSymbolAddress returned a null address");
     }
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail(ETB200_INTERNAL, cudaGetErrorString(e));
+    if (major < 10) return fail(ETB200_NOT_SUPPORTED, "this library is built for sm_100a only");
     int sms = 0;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess || sms < 1) return fail(ETB200_INTERNAL, "cannot read the SM count");
     g_sm_count[dev] = sms;
     g_scratch_ptr[dev] = p;
   }
+  if (!g_table_ready) {
+    make_exp_table(&g_table);
+    g_table_ready = true;
+  }
   *device_out = dev;
   *ptr_out = g_scratch_ptr[dev];
   *sm_count_out = g_sm_count[dev];
   return ETB200_OK;
+}
+
+// Resident blocks per SM of the sampling kernel for a dtype on a device (cached; the query
+// also opts the kernel in to its shared-memory size, which is needed once per device).
+int blocks_per_sm_cached(int dev, int dtype) {
+  const int slot = dtype == kDtypeFloat ? 0 : (dtype == kDtypeHalf ? 1 : 2);
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  if (g_blocks_per_sm[dev][slot] == 0) g_blocks_per_sm[dev][slot] = sample_kernel_max_blocks_per_sm(dtype);
+  return g_blocks_per_sm[dev][slot];
 }
 
 }  // namespace
@@ -87,9 +107,11 @@ etb200_error_t etb200_sample_rows_static(
     return fail(ETB200_NOT_SUPPORTED, "unsupported logits dtype (Half 5, Float 6, BFloat16 15, UInt16 27)");
   if (!(rows == 1 || row_stride_elems == 0 || row_stride_elems >= vocab_size))
     return fail(ETB200_INVALID_ARGUMENT, "row_stride_elems is smaller than vocab_size and not 0");
-  // the one hard limit of this entry point: at least one block's lists must fit the array
+  // the one hard limit of this entry point: at least one block's lists must fit the array.
+  // Only top-p uses the lists; argmax and multinomial calls are not limited.
+  const bool uses_lists = temperature != 0.0f && topp > 0.0f && topp < 1.0f;
   const size_t per_block = kBytesPerVocabEntryPerBlock * (size_t)vocab_size;
-  if (per_block > kStaticScratchBytes) {
+  if (uses_lists && per_block > kStaticScratchBytes) {
     char msg[200];
     snprintf(msg, sizeof(msg),
              "vocab_size %d needs %zu bytes of scratch per block, more than the %zu-byte static array "
@@ -113,15 +135,15 @@ etb200_error_t etb200_sample_rows_static(
       return fail(ETB200_NOT_SUPPORTED, "UInt16 logits can only be sampled at temperature 0");
     if (rng_states_device == nullptr)
       return fail(ETB200_INVALID_ARGUMENT, "rng_states_device is null (there is no handle to own a state)");
-    int64_t blocks = (int64_t)sms * sample_kernel_max_blocks_per_sm(dtype);
-    const int64_t fit = (int64_t)(kStaticScratchBytes / per_block);
-    if (blocks > fit) blocks = fit;
+    int64_t blocks = (int64_t)sms * blocks_per_sm_cached(dev, dtype);
+    if (uses_lists) {
+      const int64_t fit = (int64_t)(kStaticScratchBytes / per_block);
+      if (blocks > fit) blocks = fit;
+    }
     if (blocks > rows) blocks = rows;
-    ExpTable table;
-    make_exp_table(&table);
     e = launch_sample_rows(dtype, logits_device, rows, vocab_size, row_stride_elems, inv_t, topp,
                            /*topk=*/0, reinterpret_cast<unsigned long long*>(rng_states_device), out_ids_device,
-                           PeerOut{}, scratch, (int)blocks, table, nullptr, st);
+                           PeerOut{}, scratch, (int)blocks, g_table, nullptr, st);
   }
   if (e != cudaSuccess) return fail(ETB200_INTERNAL, cudaGetErrorString(e));
   return ETB200_OK;

@@ -214,9 +214,10 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_host(
  * without any allocation: the kernel's candidate lists live in a fixed 64 MiB array inside
  * the library image (every GPU that loads the library holds those 64 MiB until exit).
  *   - Runs on the CURRENT CUDA device; enqueues on `stream`; does not synchronise.
- *   - Limit: 16 * vocab_size bytes must fit the array, i.e. vocab_size <= 4194304; larger
- *     sizes are refused with ETB200_INVALID_ARGUMENT. Fewer thread blocks run at once than
- *     with a handle (32 at a 131072-entry vocabulary), so large batches are slower.
+ *   - Limit (top-p calls, the only ones that use the array): 16 * vocab_size bytes must fit
+ *     it, i.e. vocab_size <= 4194304; larger sizes are refused with ETB200_INVALID_ARGUMENT.
+ *     Fewer thread blocks run at once than with a handle (32 at a 131072-entry vocabulary), so
+ *     large top-p batches are slower. Argmax and multinomial calls are not limited.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call before starting any stream capture.
  *   - All calls share the one array. Nothing in it has to start at zero (each call writes
