@@ -44,7 +44,8 @@ FALLBACK_HBM_GBS = 6650.0
 PARITY_ROWS = 64
 KERNEL_SOURCES = ["executorch_b200/csrc/sampler_kernels.cu", "executorch_b200/csrc/guided_sum.cuh",
                   "executorch_b200/csrc/cluster_topp.cuh", "executorch_b200/csrc/cluster_math.cuh",
-                  "executorch_b200/csrc/exact_math.cuh"]
+                  "executorch_b200/csrc/exact_math.cuh", "executorch_b200/csrc/class_math.cuh",
+                  "executorch_b200/csrc/value_class_tail.cuh"]
 
 
 def kernel_source_hash():

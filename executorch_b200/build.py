@@ -18,7 +18,8 @@ LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libetb200_sampler.so")
 
 SOURCES = ["sampler_kernels.cu", "c_api.cu", "static_scratch.cu"]
-HEADERS = ["exact_math.cuh", "sampler_kernels.cuh", os.path.join("..", "..", "include", "etb200_sampler.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith(".cuh")) + [
+    os.path.join("..", "..", "include", "etb200_sampler.h")]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -25,8 +25,21 @@ __device__ long long g_phase_clock[16];
   do {                                                                      \
     if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] = clock64();  \
   } while (0)
+// time spent between the two macros, and event counts, accumulated into slot k
+#define ETB_CLOCK_BEGIN() const long long etb_clock_t0 = clock64()
+#define ETB_CLOCK_ADD(k)                                                                      \
+  do {                                                                                        \
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] += clock64() - etb_clock_t0;   \
+  } while (0)
+#define ETB_COUNT(k)                                                \
+  do {                                                              \
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] += 1; \
+  } while (0)
 #else
 #define ETB_STAMP(k)
+#define ETB_CLOCK_BEGIN()
+#define ETB_CLOCK_ADD(k)
+#define ETB_COUNT(k)
 #endif
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {

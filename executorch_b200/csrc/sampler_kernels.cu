@@ -23,10 +23,12 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #include <type_traits>
 
+#include "class_math.cuh"
 #include "cluster_math.cuh"
 #include "exact_math.cuh"
 #include "sampler_kernels.cuh"
@@ -100,14 +102,54 @@ struct GuidedShared {
 struct NoGuidedShared {};
 static_assert(kGEventCap <= kThreads, "one thread per event resolves the pending summaries");
 
+// Shared state of the value-class tail (value_class_tail.cuh): a window of class counts, later
+// reused for per-(tile, thread) member counts, and the block's walk record.
+constexpr int kVcBins = 16384;                 // value classes per window
+constexpr int kVcPer = 4;                      // classes per thread in one round of the walk
+constexpr int kVcTile = kThreads * kVcPer;
+constexpr int kVcSelTile = kThreads * 32;      // logits per tile of the final lookup
+constexpr int kVcSelTiles = kVcBins / kThreads;
+constexpr int kVcListCap = 32768;              // a 16-bit top-p row with more listed candidates takes the class tail
+constexpr int kVcListProbe = 2048;             // from this many on, the count so far is extrapolated to the whole row
+constexpr int kVcMinNucleus = 4096;            // ... and so does one whose list is short of this many, at least
+constexpr int kVcPendCap = 8;                  // deferred tails a block collects before it runs them
+constexpr int kVcCheckpoints = 6;              // window starts of one row (65536 keys / kVcBins, and one)
+static_assert(kVcPer == 4, "a thread reads its four class counts as one 128-bit word");
+
+struct VcHist {
+  alignas(16) unsigned hist[kVcBins];
+};
+struct NoVcHist {};
+struct VcControl {
+  SeqSummary wsum[kWarps], wpre[kWarps], tot;
+  int wcnt[kWarps], wpre_cnt[kWarps], tot_cnt;
+  int hit_tid, found, kb, n, hit_b, hit_j, hit_pos;
+  float cum, p;
+  int ended;
+  unsigned last_key;
+  int loaded_hi, n_ck;
+  int ck_hi[kVcCheckpoints], ck_kb[kVcCheckpoints], ck_n[kVcCheckpoints], ck_pos[kVcCheckpoints];
+  int g_lo, g_hi, token;
+  int tile_tot[kVcSelTiles];
+  // rows whose tail is deferred until the block has left its row loop (see sample_rows_kernel)
+  int n_pend;      // rows recorded in pend[]
+  int class_ok;    // the current row may take the class tail
+  float raw_max;   // the current row's largest logit
+  struct Pending {
+    long long row;
+    float inv_t, mx, sum, cutoff, topp, coin, raw_max;
+  } pend[kVcPendCap];
+};
+
 template <bool kLut, bool kGuided = false, bool kExtended = false>
 struct __align__(16) Shared {
+  static constexpr bool kHasClassTail = !kGuided;  // the guided variant keeps its shared memory for itself
+  VcControl vcc;
   // (members read with vector loads carry their own alignas)
   static constexpr bool kHasLut = kLut;
   static constexpr bool kExt = kExtended;  // per-row settings and the fused scalar multiply
   typename std::conditional<kGuided, GuidedShared, NoGuidedShared>::type g;
   uint64_t exp_tab[kExpTableSize];
-  float lut[kLut ? kLutSize : 2];
   alignas(16) float head[kHead];  // read as float4
   SeqSummary wsum[3][kWarps];  // slots used by successive scan rounds in rotation (see seqsum_tile)
   int first[2];
@@ -122,7 +164,10 @@ struct __align__(16) Shared {
   float hit_val;
   int misc_i[4];
   float misc_f[4];
-  union {
+  // The table sits directly in front of the union: the value-class tail, which needs neither,
+  // lays its window of class counts over both (vc_hist()).
+  alignas(16) float lut[kLut ? kLutSize : 4];
+  union alignas(16) {
     // terms of the row's first tile, one padded run per thread, for the one-warp start of the sum
     alignas(16) float stage[kThreads * kStagePitch];
     unsigned wbins[kWarps / 2][kBins][2];  // per warp pair and value bin: count, sum of mantissa offsets
@@ -148,6 +193,7 @@ struct __align__(16) Shared {
       unsigned wofs[kWarps][kRadix];  // per warp and digit: count, then running output offset
       unsigned above[kRadix];
     } radix;
+    typename std::conditional<(kGuided || kLut), NoVcHist, VcHist>::type vc;
   } u;
 };
 
@@ -864,8 +910,10 @@ __device__ __forceinline__ __nv_bfloat162 neg_inf2(__nv_bfloat16) {
 // Max over the row of logit * inv_t (softmax, sampler.cpp:191-196).
 template <typename T, typename S>
 __device__ __forceinline__ float row_max_scaled(
-    S& sm, const RowMath<T, S>& rm, const T* __restrict__ row, int vocab, bool vec_ok, float inv_t) {
+    S& sm, const RowMath<T, S>& rm, const T* __restrict__ row, int vocab, bool vec_ok, float inv_t,
+    float* raw_max = nullptr) {
   const int tid = threadIdx.x;
+  if (raw_max != nullptr) *raw_max = NAN;  // known only on the 16-bit path below
   if constexpr (sizeof(T) == 2) {
     if (inv_t > 0.0f) {
       // x -> fl(x * inv_t) is monotone for inv_t > 0, so the max can be taken on the raw
@@ -893,6 +941,7 @@ __device__ __forceinline__ float row_max_scaled(
       float m = fmaxf(to_f32(acc.x), to_f32(acc.y));
       for (int i = nvec * 8 + tid; i < vocab; i += kThreads) m = fmaxf(m, to_f32(row[i]));
       m = block_max(sm, m);
+      if (raw_max != nullptr) *raw_max = m;
       return __fmul_rn(rm.xform(m), inv_t);  // the multiply is by a positive factor: monotone too
     }
   }
@@ -1112,6 +1161,7 @@ __device__ bool pick_value_threshold(
       sm.misc_i[1] = chosen;
       sm.misc_i[2] = done ? 1 : 0;
       sm.misc_i[3] = chosen_cnt;
+      sm.misc_f[1] = acc;  // mass of the bins looked at (all of them when the list was not enough)
     }
   }
   __syncthreads();
@@ -1438,6 +1488,7 @@ __device__ int block_argmax(S& sm, const RowMath<T, S>& rm, int vocab) {
 }
 
 #include "guided_sum.cuh"
+#include "value_class_tail.cuh"
 
 // ---------------------------------------------------------------------------------------
 // The sampling kernel (temperature != 0): multinomial when topp is outside (0, 1), top-p
@@ -1478,7 +1529,15 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
 
   // with a row list (rows that the cluster kernel left undecided) only those rows are sampled
   const int64_t n_todo = row_list != nullptr ? (int64_t)*row_count : rows;
-  for (int64_t it = blockIdx.x; it < n_todo; it += gridDim.x) {
+  // Rows that finish in the value-class tail are only recorded inside the row loop; the block runs
+  // those tails in batches outside it. (A call inside the loop costs every row: the state that
+  // lives across it no longer fits the registers.)
+  // (The bookkeeping of this lives in shared memory: the row loop has no register to spare.)
+  if (tid == 0) sm.vcc.n_pend = 0;
+  __syncthreads();
+  int64_t it = blockIdx.x;
+  for (;;) {
+  for (; it < n_todo && sm.vcc.n_pend < kVcPendCap; it += gridDim.x) {
     const int64_t r = row_list != nullptr ? (int64_t)row_list[it] : it;
     // the row's settings: the handle's, or -- extended entry point -- its own
     // (LLMSession's SamplingConfig{temperature, top_p, top_k, seed}, llm_session.h:29-34)
@@ -1516,7 +1575,19 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
 
     ETB_STAMP(0);
     // ---- pass 1: max of the scaled logits
-    rm.mx = row_max_scaled<T>(sm, rm, rm.row, vocab, rm.vec_ok, inv_t);
+    {
+      float raw_max;
+      rm.mx = row_max_scaled<T>(sm, rm, rm.row, vocab, rm.vec_ok, inv_t, &raw_max);
+      if constexpr (sizeof(T) == 2 && S::kHasClassTail) {
+        if (tid == 0) {
+          // a 16-bit top-p row with finite logits can finish in the value-class tail
+          const bool topp_row = !(topk > 0 && topk < vocab) && !(topp <= 0.0f || topp >= 1.0f);
+          sm.vcc.raw_max = raw_max;
+          sm.vcc.class_ok = (topp_row && fabsf(raw_max) < INFINITY && fabsf(rm.mx) < INFINITY &&
+                             vocab <= kVcSelTiles * kVcSelTile) ? 1 : 0;
+        }
+      }
+    }
 
     // the coin is drawn once per sampled row (sampler.cpp:237); the guided variant stores the
     // advanced state only once it knows that it decides the row
@@ -1540,6 +1611,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
     // floor, guess) here and verify afterwards that this was enough.
     const float exact_floor0 = use_topp ? cutoff * 0.999999f : 1.4e-45f;
     const float e_floor = use_list ? fmaxf(exact_floor0, guess) : 0.0f;
+    // A 16-bit top-p row whose list outgrows kVcListCap has a long nucleus: listing stops there
+    // and the row is finished from its value classes instead (value_class_tail.cuh).
+    bool listing = use_list;  // block-uniform
     float s = 0.0f;
     int n_a = 0;
     if constexpr (kGuided) {
@@ -1624,7 +1698,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       (void)exact_floor0;
       int cnt = 0, inc = 0;
       unsigned cmask = 0;  // bit j: e[j] is a candidate
-      if (use_list) {
+      if (listing) {
         // entries beyond the row are 0 and the floor is > 0, so they never count.
         // e >= floor is e > f for the float f just below the floor; with B = 1 / ulp(f) the
         // fused e * B - f * B is >= 1 in the first case and <= 0 otherwise, so its saturation
@@ -1660,7 +1734,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       } else {
         seqsum_tile<false>(sm, e, s, rp, 0.0f, base, vocab, &hp, &hs);
       }
-      if (use_list) {
+      if (listing) {
         // candidates of the warps in front of this one, and of the whole tile
         const int wc = lane < kWarps ? sm.wcnt[buf][lane] : 0;
         const int pre = __reduce_add_sync(0xffffffffu, lane < warp ? wc : 0);
@@ -1685,14 +1759,26 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
         }
         n_a += tot;
         buf ^= 1;
+        if constexpr (sizeof(T) == 2 && S::kHasClassTail) {
+          // n_a is the same in every thread; the flag was published by the barriers since pass 1
+          // (sorting is the faster finish up to about kVcListCap candidates; candidates are
+          // spread over the row, so a dense start tells early that there will be far more)
+          const long long seen = (long long)base + kTile;
+          if (n_a > kVcListProbe && (long long)n_a * vocab > (long long)kVcListCap * seen &&
+              sm.vcc.class_ok != 0) {
+            listing = false;
+          }
+        }
       }
       if (first_tile) sum_staged_tile<false>(sm, s, 0.0f, vocab, &hp, &hs);
     }
     }  // !kGuided
     const float sum = s;
+    ETB_STAMP(2);
     __syncthreads();
     const float coin = sm.misc_f[0];
     int token;
+    bool deferred = false;  // the row finishes in the value-class tail, after the row loop
 
     if (!use_list) {
       // ---- pass 3a: sample_mult (sampler.cpp:58-70): running float cdf of p_i = e_i / S
@@ -1736,10 +1822,28 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       float cum = 0.0f;
       bool have = false, token_ready = false;
       token = 0;
+      if constexpr (sizeof(T) == 2 && S::kHasClassTail) {
+        if (!listing) {
+          // the list was abandoned: a long nucleus, finished without list or sort
+          deferred = true;
+          have = true;  // skips the rounds below
+        }
+      }
       for (int round = 0; round < 4 && !have; ++round) {
         int bin_lo = 0, kept = n_a;
         bool enough = true;
         if (!take_all) enough = pick_value_threshold(sm, listA, n_a, sum, topp, topk, use_topk, &bin_lo, &kept);
+        if constexpr (sizeof(T) == 2 && S::kHasClassTail) {
+          if (!enough && !complete && sm.vcc.class_ok != 0) {
+            // Every token that is not listed has e < e_floor, so the nucleus needs at least
+            // (missing mass) / e_floor more of them: a long nucleus takes the class tail at once.
+            const float missing = topp * sum - sm.misc_f[1];
+            if ((float)n_a + missing / e_floor > (float)kVcMinNucleus) {
+              deferred = true;
+              break;
+            }
+          }
+        }
         if (!enough && !complete) {
           guess = fmaxf(guess * 0.0625f, 1e-30f);  // later rows of this block start lower
           n_a = gather_candidates(rm, sm, listA, exact_floor);
@@ -1806,7 +1910,21 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
           take_all = true;  // the value threshold was too optimistic: take all candidates
         }
       }
-      if (token_ready) {
+      if (deferred) {
+        if (tid == 0) {
+          VcControl::Pending pd;
+          pd.row = (long long)r;
+          pd.inv_t = inv_t;
+          pd.mx = rm.mx;
+          pd.sum = sum;
+          pd.cutoff = cutoff;
+          pd.topp = topp;
+          pd.coin = coin;
+          pd.raw_max = sm.vcc.raw_max;
+          sm.vcc.pend[sm.vcc.n_pend] = pd;
+          sm.vcc.n_pend += 1;  // read again behind the barrier that ends the row
+        }
+      } else if (token_ready) {
         // decided by small_tail
       } else if (n_b <= 0 || !have) {
         token = 0;  // no candidate at all (NaN rows): undefined in the reference
@@ -1820,8 +1938,39 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
       }
     }
     ETB_STAMP(6);
-    store_token(out_ids, peers, r, token);
+    if (!deferred) store_token(out_ids, peers, r, token);
     __syncthreads();
+  }
+  if constexpr (sizeof(T) == 2 && S::kHasClassTail) {
+    // ---- the deferred value-class tails
+    const int n_pend = sm.vcc.n_pend;
+    for (int k = 0; k < n_pend; ++k) {
+      __syncthreads();
+      const VcControl::Pending pd = sm.vcc.pend[k];
+      RowMath<T, S> rm;
+      rm.row = logits + pd.row * row_stride;
+      rm.vocab = vocab;
+      rm.vec_ok = (reinterpret_cast<uintptr_t>(rm.row) & 15u) == 0;
+      rm.inv_t = pd.inv_t;
+      rm.mx = pd.mx;
+      rm.sum = 1.0f;
+      rm.probs = false;
+      if constexpr (kExt) rm.scale = ext.scale;
+      int token = value_class_tail(sm, rm, pd.sum, pd.cutoff, pd.topp, pd.coin, pd.raw_max);
+      if (token < 0) {
+        // -1: no candidate at all, undefined in the reference (token 0 like the sorted path);
+        // -2: counts that do not add up, which the host can read from the status word
+        if (token == -2 && tid == 0 && status != nullptr) atomicMax(status, kStatusTailInconsistent);
+        token = 0;
+      }
+      ETB_STAMP(6);
+      store_token(out_ids, peers, pd.row, token);
+    }
+    __syncthreads();
+  }
+  if (tid == 0) sm.vcc.n_pend = 0;
+  __syncthreads();
+  if (it >= n_todo) break;
   }
   peer_arrival_barrier(peers, status);
 }
@@ -2222,6 +2371,10 @@ cudaError_t launch_topp_cluster(
 #if defined(ETB200_PHASE_CLOCKS)
 extern "C" __attribute__((visibility("default"))) int etb200_debug_phase_clocks(long long* out16) {
   return (int)cudaMemcpyFromSymbol(out16, g_phase_clock, sizeof(long long) * 16);
+}
+extern "C" __attribute__((visibility("default"))) int etb200_debug_phase_clocks_reset() {
+  const long long zero[16] = {0};
+  return (int)cudaMemcpyToSymbol(g_phase_clock, zero, sizeof(zero));
 }
 #endif
 

@@ -121,6 +121,7 @@ cudaError_t launch_argmax_rows(
 
 // Value stored into `status` when the arrival barrier of PeerOut gave up waiting for a rank.
 constexpr int kStatusPeerTimeout = 2;
+constexpr int kStatusTailInconsistent = 3;  // the long-nucleus tail's final lookup found its counts inconsistent
 
 // y[i] = expf_ref(x[i]) on the device, for x <= 0: lets a test compare the device
 // exponential with the host libm.

@@ -194,7 +194,9 @@ ETB200_EXPORT etb200_error_t etb200_sampler_sample_rows_exchange(
 ETB200_EXPORT etb200_error_t etb200_sampler_set_wait_limit_ns(etb200_sampler_t* handle, uint64_t nanoseconds);
 
 /* Reads and clears the handle's device status word (synchronises): 0 = nothing to report,
- * 2 = the arrival wait of etb200_sampler_sample_rows_exchange ran out for some rank. */
+ * 2 = the arrival wait of etb200_sampler_sample_rows_exchange ran out for some rank,
+ * 3 = an internal consistency check of the long-nucleus top-p tail failed for some row since
+ * the last read (that row's id is 0 and not to be trusted; not expected to happen). */
 ETB200_EXPORT etb200_error_t etb200_sampler_get_status(etb200_sampler_t* handle, int32_t* out_status);
 
 /* Same as etb200_sampler_sample_rows for callers whose logits live in HOST memory (what

@@ -1,0 +1,89 @@
+"""16-bit rows with a LONG nucleus (tens of thousands of tokens pass the cutoff crop of
+sampler.cpp:136-143): the CUDA sampler takes its value-class tail for them (no candidate list, no
+sort). Tokens must be identical to the oracle's, which sorts the candidates as the reference does
+(equal probabilities by index)."""
+import numpy as np
+import pytest
+import torch
+
+from executorch_b200 import Sampler, seeds_to_states
+from executorch_b200 import workloads as W
+
+from parity import gpu_sample
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(v, dtype):
+    return W.f32_to_bf16_bits(v) if dtype == "bf16" else v.astype(np.float16).view(np.uint16)
+
+
+def _rows(rng, kind, vocab):
+    if kind == "flat":
+        return (0.05 * rng.standard_normal(vocab)).astype(np.float32)
+    if kind == "peaked":
+        v = rng.standard_normal(vocab).astype(np.float32)
+        hot = rng.choice(vocab, 5, replace=False)
+        v[hot[0]] = 12.0
+        v[hot[1:]] = 8.0
+        return v
+    if kind == "quantised":   # few distinct values: classes of thousands of tokens
+        return (np.round(rng.standard_normal(vocab) * 4) / 4).astype(np.float32)
+    if kind == "constant":    # one class holds the whole row
+        return np.full(vocab, 1.25, dtype=np.float32)
+    if kind == "masked":      # a logit processor masked most tokens
+        v = (0.3 * rng.standard_normal(vocab)).astype(np.float32)
+        v[rng.random(vocab) < 0.6] = -np.inf
+        return v
+    if kind == "signs":       # values around zero: both signs, zeros of both signs, subnormals
+        v = (1e-4 * rng.standard_normal(vocab)).astype(np.float32)
+        v[::17] = 0.0
+        v[5::17] = -0.0
+        return v
+    raise ValueError(kind)
+
+
+KINDS = ("flat", "peaked", "quantised", "constant", "masked", "signs")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_long_nucleus_rows_match_the_oracle(cuda_device, restatement, dtype):
+    rng = np.random.default_rng(31)
+    for vocab in (151_936, 50_001, 3_000):
+        reps = 6
+        x = np.stack([_bits(_rows(rng, k, vocab), dtype) for k in KINDS for _ in range(reps)])
+        seeds = rng.integers(0, 2**62, size=len(x)).astype(np.uint64)
+        for t, p in ((1.0, 0.9), (1.3, 0.5), (0.8, 0.999), (2.0, 0.05)):
+            want = restatement.sample_rows(x, t, p, seeds, dtype=dtype, threads=16)
+            got = gpu_sample(x, dtype, t, p, seeds, cuda_device)
+            bad = np.nonzero(got != want)[0]
+            assert len(bad) == 0, (dtype, vocab, t, p, [(int(r), KINDS[r // reps]) for r in bad[:8]])
+
+
+def test_many_draws_on_one_flat_and_one_peaked_row(cuda_device, restatement):
+    """The coin sweeps the whole cumulative distribution: every window of classes gets hits."""
+    rng = np.random.default_rng(32)
+    vocab = 151_936
+    for kind in ("flat", "peaked"):
+        row = _bits(_rows(rng, kind, vocab), "fp16")
+        x = np.tile(row, (512, 1))
+        seeds = rng.integers(0, 2**62, size=512).astype(np.uint64)
+        want = restatement.sample_rows(x, 1.0, 0.9, seeds, dtype="fp16", threads=16)
+        got = gpu_sample(x, "fp16", 1.0, 0.9, seeds, cuda_device)
+        assert np.array_equal(got, want), (kind, np.nonzero(got != want)[0][:8])
+
+
+def test_misaligned_strided_view(cuda_device, restatement):
+    rng = np.random.default_rng(33)
+    vocab, rows, pitch = 40_001, 6, 40_960 + 3
+    v = (0.05 * rng.standard_normal((rows, pitch))).astype(np.float32)
+    for dtype, tdt in (("fp16", torch.float16), ("bf16", torch.bfloat16)):
+        base = torch.from_numpy(v).to(cuda_device).to(tdt)
+        view = base[:, 1:1 + vocab]
+        xh = view.contiguous().cpu().view(torch.int16).numpy().view(np.uint16)
+        seeds = np.arange(rows, dtype=np.uint64) + 9
+        s = Sampler(vocab, 1.0, 0.9, 0, device=cuda_device)
+        got = s.sample_rows(view, seeds_to_states(seeds, cuda_device)).cpu().numpy()
+        s.close()
+        want = restatement.sample_rows(xh, 1.0, 0.9, seeds, dtype=dtype)
+        assert np.array_equal(got, want), dtype
