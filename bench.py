@@ -71,10 +71,20 @@ def dram_traffic(kernel: str):
         return None, True
 
 
-def config_dict(gpus: int, greedy: bool, exchange: str):
+def config_dict(gpus: int, greedy: bool, exchange: str, workload: str = WORKLOAD):
     """The `config` object; the same for both arms of the benchmark."""
     from executorch_b200 import workloads as W
-    cfg = W.CONFIGS[WORKLOAD]
+    cfg = W.CONFIGS[workload]
+    if workload == "c5":
+        # strong scaling: the configuration's 32 768 rows are divided among the GPUs
+        per = cfg.rows // gpus
+        return {
+            "workload": f"c5: {cfg.rows} rows x V={cfg.vocab} bf16 Zipf logits in all, T={cfg.temperature}, "
+                        f"top-p {cfg.topp}, seed=row; rows divided evenly among the GPUs",
+            "rows_per_gpu": per, "vocab": cfg.vocab, "global_rows": per * gpus,
+            "l2": f"one input batch per GPU ({per * cfg.vocab * 2 / 1e9:.1f} GB > 126 MB L2)",
+            "exchange": "none (ids stay on the GPU that sampled them)",
+        }
     names = {"p2p": "ids stored into every peer's buffer by the kernel epilogue + symmetric-memory barrier on a "
                     "side stream",
              "p2p-in-kernel": "ids stored into every peer's buffer by the kernel epilogue + arrival marks and a "
@@ -184,11 +194,12 @@ def run_reference(args, rank, world):
         return
     import numpy as np
     from executorch_b200 import workloads as W
-    cfg = W.CONFIGS[WORKLOAD]
-    rows = cfg.rows
+    workload = args.workload
+    cfg = W.CONFIGS[workload]
+    rows = 256  # the batch a step draws its rows from (c3: the whole batch)
     # same distribution as the device-born benchmark rows; a 64-row host sample tiled to the
     # batch keeps generation short (the sampler's cost does not depend on which rows repeat)
-    base = W.rows_numpy(WORKLOAD, list(range(64)))
+    base = W.rows_numpy(workload, list(range(64)))
     x = np.ascontiguousarray(np.tile(base, (rows // 64, 1)))
     seeds = np.arange(rows, dtype=np.uint64)
     threads = os.cpu_count() or 1
@@ -212,11 +223,13 @@ def run_reference(args, rank, world):
         w, _, _ = cpu_reference_pass(x[:n], cfg, seeds[:n], thr, native=nat)
         variants[label] = {"rows_per_s": n / w, "threads": thr, "rows": n}
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
+        "impl": "reference",
+        "metric": "sampled_rows_per_s_topp_v256000_bf16" if workload == "c5" else METRIC,
+        "value": value, "unit": "rows/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "logits_dtype": "bf16", "data": "synthetic",
-        "config": config_dict(args.gpus, False, args.exchange),
+        "higher_is_better": True, "scaling": "strong" if workload == "c5" else "weak", "vs_baseline": None,
+        "dtype": "f32", "logits_dtype": "bf16", "data": "synthetic",
+        "config": config_dict(args.gpus, False, args.exchange, workload),
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": kind,
                          "sample": f"each step = {per_step} rows of the {rows}-row batch on {threads} threads; {how}",
                          "variants": variants},
@@ -292,6 +305,9 @@ def main():
     ap.add_argument("--no-other-configs", action="store_true")
     ap.add_argument("--kernel", type=int, default=0, choices=[0, 1, 2, 3],
                     help="kernel choice of the handle (0 = automatic; see etb200_sampler_set_kernel_choice)")
+    ap.add_argument("--workload", default=WORKLOAD, choices=["c3", "c5"],
+                    help="c3 (default): the headline batch, 256 rows per GPU, weak scaling. c5: 32768 rows x "
+                         "V=256000 divided among the GPUs (16.8 GB in all), strong scaling, no id exchange")
     ap.add_argument("--greedy", action="store_true",
                     help="config 3's second pass instead of the headline: temperature 0 (argmax) on the same batch")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-in-kernel", "nccl"],
@@ -321,13 +337,20 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    cfg = W.CONFIGS[WORKLOAD]
-    rows, vocab = cfg.rows, cfg.vocab
+    workload = args.workload
+    strong = workload == "c5"
+    cfg = W.CONFIGS[workload]
+    rows, vocab = (cfg.rows // world if strong else cfg.rows), cfg.vocab
     total_rows = rows * world
     warmup = max(args.warmup, 3)
+    nbuf = 1 if strong else NBUF  # one c5 shard alone is far larger than L2
+    if strong:
+        args.greedy = False
+        args.no_cpu_baseline = args.no_other_configs = True
+        args.exchange = "nccl"  # unused: no exchange in this workload
 
-    # inputs born in HBM: NBUF distinct batches for this rank (rows are a function of their id)
-    bufs = [W.rows_torch(WORKLOAD, (rank * NBUF + b) * rows, rows, dev) for b in range(NBUF)]
+    # inputs born in HBM: nbuf distinct batches for this rank (rows are a function of their id)
+    bufs = [W.rows_torch(workload, (rank * nbuf + b) * rows, rows, dev) for b in range(nbuf)]
     seeds = np.arange(rank * rows, (rank + 1) * rows, dtype=np.uint64)
     states0 = seeds_to_states(seeds, dev)
     states = states0.clone()
@@ -339,7 +362,7 @@ def main():
         args.no_cpu_baseline = True
 
     exchange, exchange_mode = None, (args.exchange if world > 1 else "none")
-    if world > 1 and args.exchange in ("p2p", "p2p-in-kernel"):
+    if world > 1 and not strong and args.exchange in ("p2p", "p2p-in-kernel"):
         try:
             from executorch_b200.sharded import PeerIdExchange
             exchange = PeerIdExchange(total_rows, dev)
@@ -361,23 +384,23 @@ def main():
         if k_start is not None:
             k_start.record()
         if exchange is not None and in_kernel_sync:
-            sampler.sample_rows_exchange(bufs[i % NBUF], states, exchange.dest_ptrs, exchange.mark_ptrs, rank,
+            sampler.sample_rows_exchange(bufs[i % nbuf], states, exchange.dest_ptrs, exchange.mark_ptrs, rank,
                                          rank * rows, exchange.next_epoch())
             if k_end is not None:
                 k_end.record()
             return exchange.finish(barrier=False)
         if exchange is not None:
-            sampler.sample_rows_scatter(bufs[i % NBUF], states, exchange.dest_ptrs, rank * rows)
+            sampler.sample_rows_scatter(bufs[i % nbuf], states, exchange.dest_ptrs, rank * rows)
             if k_end is not None:
                 k_end.record()
             # the barrier runs on a side stream: the next step's launch does not queue behind it
             return exchange.finish(overlap=True)[0]
-        sampler.sample_rows(bufs[i % NBUF], states, out=local_ids)
+        sampler.sample_rows(bufs[i % nbuf], states, out=local_ids)
         if k_end is not None:
             k_end.record()
-        if world > 1:
+        if world > 1 and not strong:
             dist.all_gather_into_tensor(all_ids, local_ids)
-        return all_ids
+        return local_ids if strong else all_ids
 
     for i in range(warmup):
         states.copy_(states0)
@@ -421,16 +444,16 @@ def main():
 
     # ---- parity: one more step, from known states, checked outside the timed region
     import oracle
-    vb = args.steps % NBUF
+    vb = args.steps % nbuf
     states.copy_(states0)
     got_all = step(args.steps)
     if exchange is not None:
         exchange.drain()
     torch.cuda.synchronize()
     got_all = got_all.clone()
-    mine = got_all[rank * rows:(rank + 1) * rows] if world > 1 else got_all
+    mine = got_all[rank * rows:(rank + 1) * rows] if (world > 1 and not strong) else got_all
     exchange_verified = None
-    if world > 1:
+    if world > 1 and not strong:
         # every rank's own ids of the same step, gathered by NCCL: the exchange must agree
         ref_all = torch.empty(total_rows, dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(ref_all, mine.contiguous())
@@ -447,10 +470,12 @@ def main():
         parity_rows, parity_equal = PARITY_ROWS, int((gh == want).sum())
 
     # ---- end to end through the host-buffer entry of the C ABI (pinned host logits)
-    host_bufs = [b.cpu().view(torch.int16).pin_memory().view(torch.bfloat16) for b in bufs[:2]]
-    host_states = seeds.copy()
+    e2e_rows = min(rows, 1024) if strong else rows  # c5: a slice (a whole shard is gigabytes per step)
+    host_bufs = [bufs[b % nbuf][:e2e_rows].cpu().view(torch.int16).pin_memory().view(torch.bfloat16)
+                 for b in range(2)]
+    host_states = seeds[:e2e_rows].copy()
     for i in range(2):
-        host_states[:] = seeds
+        host_states[:] = seeds[:e2e_rows]
         sampler.sample_rows_host(host_bufs[i % 2], host_states)
     if world > 1:
         dist.barrier()
@@ -463,24 +488,26 @@ def main():
         tt = torch.tensor([e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e_ms = float(tt[0])
-    e2e_value = total_rows * args.e2e_steps / (e_ms * 1e-3)
-    h2d = rows * vocab * 2 + rows * 8
-    d2h = rows * 8 + rows * 8
-    assert ids_host.shape == (rows,)
+    e2e_value = e2e_rows * world * args.e2e_steps / (e_ms * 1e-3)
+    h2d = e2e_rows * vocab * 2 + e2e_rows * 8
+    d2h = e2e_rows * 8 + e2e_rows * 8
+    assert ids_host.shape == (e2e_rows,)
 
     if rank == 0:
         peak, which = hbm_peak()
         algo_bytes = rows * (vocab * 2 + 8 + 16)  # logits once + id + rng state in/out
         achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
         kernel_name = "argmax_rows_kernel" if args.greedy else "sample_rows_kernel"
-        traffic, stale = dram_traffic(kernel_name)
+        traffic, stale = dram_traffic(kernel_name) if not strong else (None, False)
         line = {
-            "metric": "argmax_rows_per_s_v128256_bf16" if args.greedy else METRIC,
+            "metric": ("sampled_rows_per_s_topp_v256000_bf16" if strong else
+                       "argmax_rows_per_s_v128256_bf16" if args.greedy else METRIC),
             "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "logits_dtype": "bf16",
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32",
+            "logits_dtype": "bf16",
             "data": "synthetic",
-            "config": config_dict(world, args.greedy, exchange_mode if world > 1 else args.exchange),
+            "config": config_dict(world, args.greedy, exchange_mode if world > 1 else args.exchange, workload),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "traffic_stale": stale,
                          "peak_source": f"of {which}", "kernel_ms": kernel_ms, "kernel": kernel_name,
@@ -488,7 +515,8 @@ def main():
             "parity": {"checked_rows": parity_rows, "equal": parity_equal, "exchange_verified": exchange_verified,
                        "against": "CPU oracle (C restatement of sampler.cpp) on the rows of one extra step"},
             "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / args.e2e_steps},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / args.e2e_steps,
+                    "rows_per_step_per_gpu": e2e_rows},
             "gpu_launches": int(launches),
             "clocks": clock_info,
         }
