@@ -49,15 +49,19 @@ constexpr int kFThreads = 256;
 constexpr int kFEventCap = 448;
 constexpr int kFPoolCap = 192;
 constexpr int kFCandCap = 1024;
+constexpr int kFSerialWalk = 256;   // lists up to this many records are replayed record by record
 
-struct SliceHeader {
+struct __align__(16) SliceHeader {
   int n_events;  // records written, including the closing one; 0 = the slice gave up
   int n_cand;
-  int pad0, pad1;
+  int n_staged;  // staged chunks: their terms are terms[0 .. n_staged), in event order
+  int pad;
+  unsigned long long x_total;  // the closing record's xbefore: increments of the slice's ordinary chunks
+  unsigned long long pad2;
 };
 
-// Scratch of one slice in global memory. The 32 terms of event i (if it is staged) are in
-// terms[i].
+// Scratch of one slice in global memory. A staged event's record holds the row of `terms` with
+// its 32 terms in `pool`.
 struct SliceScratch {
   SliceHeader hdr;
   ChunkEvent events[kCSliceEvents];
@@ -78,6 +82,7 @@ struct __align__(128) ClusterShared {
   double wtot[kCWarps];
   unsigned long long wx[kCWarps];
   int wev[kCWarps];
+  int wst[kCWarps];
   int wklo[kCWarps];
   int lcand_count;
   Entry lcand[kCSliceCand];  // this slice's candidates, before they go to global memory
@@ -143,6 +148,8 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
   const int len16 = len & ~7;  // whole 16-byte units go by the bulk copy
 
   ETB_STAMP(0);
+  ETB_GSTAMP(13);
+  grid_launch_dependents();  // the finishing kernel may take its place; it waits for this grid
   // ---- phase 0: the slice comes in; everything that does not need it meanwhile
   if (tid < kExpTableSize) sm.exp_tab[tid] = table.t[tid];
   if (tid == 0) {
@@ -337,23 +344,28 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     if (lane >= d) inc_incl += o;
   }
   const unsigned evb = __ballot_sync(0xffffffffu, event);
+  const unsigned stb = __ballot_sync(0xffffffffu, event && staged);
   if (lane == 31) {
     sm.wx[warp] = (unsigned long long)inc_incl;
     sm.wev[warp] = __popc(evb);
+    sm.wst[warp] = __popc(stb);
   }
   __syncthreads();
   unsigned long long x_pre = 0ull, x_tot = 0ull;
-  int ev_pre = 0, ev_tot = 0;
+  int ev_pre = 0, ev_tot = 0, st_pre = 0, st_tot = 0;
 #pragma unroll
   for (int w = 0; w < kCWarps; ++w) {
     const unsigned long long xv = sm.wx[w];
     const int c = sm.wev[w];
+    const int sc = sm.wst[w];
     if (w < warp) {
       x_pre += xv;
       ev_pre += c;
+      st_pre += sc;
     }
     x_tot += xv;
     ev_tot += c;
+    st_tot += sc;
   }
   const int n_lc = sm.lcand_count;
   const bool fits = ev_tot + 1 <= kCSliceEvents && n_lc <= kCSliceCand && copy_ok;
@@ -361,14 +373,18 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
     SliceHeader h;
     h.n_events = fits ? ev_tot + 1 : 0;
     h.n_cand = fits ? n_lc : 0;
-    h.pad0 = h.pad1 = 0;
+    h.n_staged = fits ? st_tot : 0;
+    h.pad = 0;
+    h.x_total = x_tot;
+    h.pad2 = 0ull;
     out.hdr = h;
   }
   if (fits) {
     if (event) {
       const int slot = ev_pre + __popc(evb & ((1u << lane) - 1u));
+      const int st_slot = st_pre + __popc(stb & ((1u << lane) - 1u));
       if (staged) {
-        float4* dst = reinterpret_cast<float4*>(out.terms[slot]);
+        float4* dst = reinterpret_cast<float4*>(out.terms[st_slot]);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           float e[8];
@@ -382,7 +398,7 @@ __global__ void __launch_bounds__(kCThreads, 2) topp_cluster_kernel(
       rec.a0hi = rec.a1hi = inc_hi;
       rec.xbefore = x_pre + (unsigned long long)(inc_incl - inc_mine);
       rec.klo = (short)klo;
-      rec.pool = (short)(staged ? slot : -1);
+      rec.pool = (short)(staged ? st_slot : -1);
       rec.flags = (unsigned short)flags;
       rec.pad = 0;
       out.events[slot] = rec;
@@ -421,13 +437,11 @@ struct __align__(16) FinishShared {
     FinishTail tail;  // after it
   };
   Entry cand[kFCandCap];
-  int ev_first[kCMaxCluster];
-  int ev_count[kCMaxCluster];
-  int cand_first[kCMaxCluster];
-  int cand_count[kCMaxCluster];
-  int warp_staged[kFThreads / 32];
+  int ev_first[kCMaxCluster + 1];    // slot of each slice's first record; [csize] = all records
+  int cand_first[kCMaxCluster + 1];
+  int st_first[kCMaxCluster + 1];    // the same for staged chunks
+  unsigned long long xbase[kCMaxCluster];  // increments of the ordinary chunks in front of each slice
   int ok;
-  int n_staged;
   float sum;
   float coin;
   int n_kept;
@@ -446,94 +460,106 @@ __global__ void __launch_bounds__(kFThreads) topp_finish_kernel(
   const int64_t rl = blockIdx.x;    // row inside this launch
   const int64_t r = row0 + rl;      // row of the batch
   const SliceScratch* sl0 = scratch + rl * csize;
-  ETB_STAMP(6);
   // the counter the NEXT call will use is cleared here (calls of a handle are ordered)
+  grid_launch_dependents();  // the pass over undecided rows may take its place
+  grid_dependency_wait();    // the cluster kernel's records are complete and visible from here on
+  ETB_GSTAMP(14);
+  ETB_STAMP(6);
   if (blockIdx.x == 0 && tid == 0 && retry_count_next != nullptr) *retry_count_next = 0;
 
-  // ---- the slices' headers, and where each slice's records go
-  if (tid == 0) {
-    int e = 0, c = 0;
-    bool ok = true;
-    for (int s = 0; s < csize; ++s) {
-      const SliceHeader h = sl0[s].hdr;
-      if (h.n_events < 1 || h.n_events > kCSliceEvents || h.n_cand < 0 || h.n_cand > kCSliceCand) ok = false;
-      sm.ev_first[s] = e;
-      sm.ev_count[s] = ok ? h.n_events : 0;
-      sm.cand_first[s] = c;
-      sm.cand_count[s] = ok ? h.n_cand : 0;
-      if (ok) {
-        e += h.n_events;
-        c += h.n_cand;
+  // ---- the slices' headers, all at once: where each slice's records, candidates and staged
+  // terms go, and the increments in front of each slice
+  if (warp == 0) {
+    SliceHeader h;
+    h.n_events = h.n_cand = h.n_staged = 0;
+    h.x_total = 0ull;
+    if (lane < csize) {
+      const uint4* hp = reinterpret_cast<const uint4*>(&sl0[lane].hdr);
+      const uint4 a = __ldg(hp), b = __ldg(hp + 1);
+      h.n_events = (int)a.x;
+      h.n_cand = (int)a.y;
+      h.n_staged = (int)a.z;
+      h.x_total = (unsigned long long)b.x | ((unsigned long long)b.y << 32);
+    }
+    const bool bad = lane < csize && (h.n_events < 1 || h.n_events > kCSliceEvents || h.n_cand < 0 ||
+                                      h.n_cand > kCSliceCand || h.n_staged < 0 || h.n_staged > h.n_events);
+    bool ok = !__any_sync(0xffffffffu, bad);
+    int e = h.n_events, c = h.n_cand, st = h.n_staged;
+    unsigned long long x = h.x_total;
+#pragma unroll
+    for (int d = 1; d < kCMaxCluster; d <<= 1) {
+      const int oe = __shfl_up_sync(0xffffffffu, e, d), oc = __shfl_up_sync(0xffffffffu, c, d);
+      const int os = __shfl_up_sync(0xffffffffu, st, d);
+      const unsigned long long ox = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) {
+        e += oe;
+        c += oc;
+        st += os;
+        x += ox;
       }
     }
-    if (e > kFEventCap || c > kFCandCap) ok = false;
-    sm.ok = ok ? 1 : 0;
-    sm.n_kept = 0;
-    sm.first_above = 0x7fffffff;
-    sm.n_staged = 0;
-    unsigned long long st = rng_states[r];
-    sm.coin = next_coin(&st);  // the state is stored only when the row is decided
+    // inclusive sums -> the slot behind each slice; slot 0 is 0
+    if (lane < csize) {
+      sm.ev_first[lane + 1] = e;
+      sm.cand_first[lane + 1] = c;
+      sm.st_first[lane + 1] = st;
+      sm.xbase[lane] = x - h.x_total;
+    }
+    if (lane == csize - 1 && (e > kFEventCap || c > kFCandCap)) ok = false;
+    ok = !__any_sync(0xffffffffu, !ok);
+    if (lane == 0) {
+      sm.ev_first[0] = sm.cand_first[0] = sm.st_first[0] = 0;
+      sm.ok = ok ? 1 : 0;
+      sm.n_kept = 0;
+      sm.first_above = 0x7fffffff;
+      unsigned long long rs = rng_states[r];
+      sm.coin = next_coin(&rs);  // the state is stored only when the row is decided
+    }
   }
   __syncthreads();
   bool decided = sm.ok != 0;
   int n_c = 0;
   if (decided) {
-    // ---- records, candidates and the staged terms into shared memory
-    for (int s = 0; s < csize; ++s) {
-      const int ne = sm.ev_count[s], e0 = sm.ev_first[s];
-      const uint4* src = reinterpret_cast<const uint4*>(sl0[s].events);
-      uint4* dst = reinterpret_cast<uint4*>(sm.w.events + e0);
-      for (int i = tid; i < ne * 2; i += kFThreads) dst[i] = __ldg(src + i);
-      const int nc = sm.cand_count[s], c0 = sm.cand_first[s];
-      for (int i = tid; i < nc; i += kFThreads) sm.cand[c0 + i] = sl0[s].cand[i];
+    // ---- records, candidates and the staged terms into shared memory, every load in flight at
+    // once. A record's `xbefore` runs on over the slices (a slice's closing record carries the
+    // increments of its trailing run, so every closing record but the last becomes an empty
+    // record of the run it closes); its `pool` becomes the row-wide slot of its staged terms.
+    const int n_ev = sm.ev_first[csize];
+    n_c = sm.cand_first[csize];
+    const int n_st = sm.st_first[csize] < kFPoolCap ? sm.st_first[csize] : kFPoolCap;
+    auto slice_of = [&](const int* first, int i) {
+      int sl = 0;
+      while (sl + 1 < csize && i >= first[sl + 1]) ++sl;
+      return sl;
+    };
+    for (int i = tid; i < n_ev; i += kFThreads) {
+      const int sl = slice_of(sm.ev_first, i);
+      const uint4* src = reinterpret_cast<const uint4*>(&sl0[sl].events[i - sm.ev_first[sl]]);
+      union {
+        uint4 q[2];
+        ChunkEvent ev;
+      } u;
+      u.q[0] = __ldg(src);
+      u.q[1] = __ldg(src + 1);
+      u.ev.xbefore += sm.xbase[sl];
+      if (u.ev.pool >= 0) {
+        const int slot = sm.st_first[sl] + (int)u.ev.pool;
+        u.ev.pool = (short)(slot < kFPoolCap ? slot : -1);  // no room: the replay gives up if it needs them
+      }
+      sm.w.events[i] = u.ev;
     }
-    n_c = sm.cand_first[csize - 1] + sm.cand_count[csize - 1];
+    for (int i = tid; i < n_c; i += kFThreads) {
+      const int sl = slice_of(sm.cand_first, i);
+      sm.cand[i] = sl0[sl].cand[i - sm.cand_first[sl]];
+    }
+    for (int q = tid; q < n_st * 8; q += kFThreads) {
+      const int k = q >> 3;
+      const int sl = slice_of(sm.st_first, k);
+      const float4* src = reinterpret_cast<const float4*>(sl0[sl].terms[k - sm.st_first[sl]]);
+      reinterpret_cast<float4*>(sm.w.pool[k])[q & 7] = __ldg(src + (q & 7));
+    }
     __syncthreads();
-    // staged chunks get consecutive pool slots, in event order
-    const int n_ev = sm.ev_first[csize - 1] + sm.ev_count[csize - 1];
-    int pre = 0;
-    for (int base = 0; base < n_ev; base += kFThreads) {
-      const int i = base + tid;
-      const bool st = i < n_ev && sm.w.events[i].pool >= 0;
-      const unsigned b = __ballot_sync(0xffffffffu, st);
-      if (lane == 0) sm.warp_staged[warp] = __popc(b);
-      __syncthreads();
-      int mine = pre;
-      for (int w = 0; w < kFThreads / 32; ++w) {
-        if (w < warp) mine += sm.warp_staged[w];
-        pre += sm.warp_staged[w];
-      }
-      if (st) {
-        const int slot = mine + __popc(b & ((1u << lane) - 1u));
-        // which slice this record came from
-        int s = 0;
-        while (s + 1 < csize && i >= sm.ev_first[s + 1]) ++s;
-        const int local = i - sm.ev_first[s];
-        if (slot < kFPoolCap) {
-          const float4* src = reinterpret_cast<const float4*>(sl0[s].terms[local]);
-          float4* dst = reinterpret_cast<float4*>(sm.w.pool[slot]);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) dst[k] = __ldg(src + k);
-          sm.w.events[i].pool = (short)slot;
-        } else {
-          sm.w.events[i].pool = -1;  // no room: the replay gives up if it needs these terms
-        }
-      }
-      __syncthreads();
-    }
     ETB_STAMP(7);
-    // The slices' records become one list: a slice's closing record carries the increment of
-    // its trailing run, so adding the totals of the slices in front makes `xbefore` run on,
-    // and every closing record but the last turns into an empty record of the run it closes.
-    if (tid == 0) {
-      unsigned long long base = 0ull;
-      for (int s = 0; s < csize; ++s) {
-        const int e0 = sm.ev_first[s], ne = sm.ev_count[s];
-        for (int i = 0; i < ne; ++i) sm.w.events[e0 + i].xbefore += base;
-        base = sm.w.events[e0 + ne - 1].xbefore;
-      }
-    }
-    __syncthreads();
     // ---- pending two-parity summaries: one thread per event, side by side
     for (int i = tid; i < n_ev; i += kFThreads) {
       ChunkEvent* e = &sm.w.events[i];
@@ -543,7 +569,16 @@ __global__ void __launch_bounds__(kFThreads) topp_finish_kernel(
     // ---- the exact sequential sum, replayed by one warp
     if (warp == 0) {
       float s = 0.0f;
-      const bool ok = walk_events_warp(sm.w.events, n_ev, sm.w.pool, kFPoolCap, &s);
+      bool ok;
+      if (n_ev <= kFSerialWalk) {
+        // a short list (the usual case): record by record costs less than the scans of the warp
+        // form, whose every stop at a chunk that needs real additions is a whole scan round
+        const int first = 0;
+        ok = walk_events(sm.w.events, &first, &n_ev, 1, kFEventCap,
+                         [&](int slot, int j) { return sm.w.pool[slot][j]; }, &s);
+      } else {
+        ok = walk_events_warp(sm.w.events, n_ev, sm.w.pool, kFPoolCap, &s);
+      }
       if (lane == 0) {
         sm.sum = s;
         sm.ok = ok ? 1 : 0;

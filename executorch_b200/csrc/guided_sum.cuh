@@ -31,6 +31,15 @@ __device__ long long g_phase_clock[16];
   do {                                                                                        \
     if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] += clock64() - etb_clock_t0;   \
   } while (0)
+// the GPU's global timer (nanoseconds), comparable between kernels and SMs
+#define ETB_GSTAMP(k)                                                                   \
+  do {                                                                                  \
+    if (blockIdx.x == 0 && threadIdx.x == 0) {                                          \
+      unsigned long long etb_gt;                                                        \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(etb_gt));                        \
+      g_phase_clock[k] = (long long)etb_gt;                                             \
+    }                                                                                   \
+  } while (0)
 #define ETB_COUNT(k)                                                \
   do {                                                              \
     if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[k] += 1; \
@@ -39,8 +48,17 @@ __device__ long long g_phase_clock[16];
 #define ETB_STAMP(k)
 #define ETB_CLOCK_BEGIN()
 #define ETB_CLOCK_ADD(k)
+#define ETB_GSTAMP(k)
 #define ETB_COUNT(k)
 #endif
+
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs. It must wait here before it touches
+// anything the predecessor writes (the wait ends when the predecessor's grid has completed and
+// its writes are visible; without the attribute it returns at once). The predecessor lets its
+// dependents become resident early with grid_launch_dependents().
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);

@@ -26,6 +26,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "class_math.cuh"
@@ -1527,7 +1528,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(
   Entry* listA = scratch + (size_t)blockIdx.x * 2 * (size_t)vocab;
   Entry* listB = listA + vocab;
 
-  // with a row list (rows that the cluster kernel left undecided) only those rows are sampled
+  // with a row list (rows that the cluster kernel left undecided) only those rows are sampled;
+  // that launch may have become resident before the kernel that writes the list has ended
+  if (row_list != nullptr) {
+    grid_dependency_wait();
+    ETB_GSTAMP(15);
+  }
   const int64_t n_todo = row_list != nullptr ? (int64_t)*row_count : rows;
   // Rows that finish in the value-class tail are only recorded inside the row loop; the block runs
   // those tails in batches outside it. (A call inside the loop costs every row: the state that
@@ -2112,6 +2118,30 @@ cudaError_t launch_expf_selftest(const float* x, float* y, int64_t n, const ExpT
   return cudaGetLastError();
 }
 
+// cudaFuncSetAttribute is needed once per function and device, not once per launch (the batch-1
+// decode loop launches three kernels per token: the host side of a launch matters there).
+struct OncePerDevice {
+  std::atomic<unsigned long long> mask{0ull};
+};
+static cudaError_t func_attr_once(OncePerDevice& once, const void* func, cudaFuncAttribute attr, int value) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = dev < 64 ? 1ull << dev : 0ull;
+  if (bit != 0ull && (once.mask.load(std::memory_order_acquire) & bit) != 0ull) return cudaSuccess;
+  e = cudaFuncSetAttribute(func, attr, value);
+  if (e == cudaSuccess && bit != 0ull) once.mask.fetch_or(bit, std::memory_order_release);
+  return e;
+}
+
+// Launch attribute of a kernel that may become resident while its predecessor in the stream
+// still runs; such a kernel calls grid_dependency_wait() before it touches anything the
+// predecessor writes.
+static void programmatic_launch(cudaLaunchAttribute* attr) {
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+}
+
 size_t sampler_scratch_bytes(int vocab, int blocks) {
   return (size_t)blocks * 2 * (size_t)vocab * sizeof(Entry);
 }
@@ -2122,8 +2152,9 @@ int sampler_threads() { return kThreads; }
 // cheap and idempotent).
 template <typename T, bool kLut, bool kGuided = false>
 static cudaError_t prepare_sample_kernel() {
-  return cudaFuncSetAttribute(sample_rows_kernel<T, kLut, kGuided>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)sizeof(Shared<kLut, kGuided>));
+  static OncePerDevice once;
+  return func_attr_once(once, reinterpret_cast<const void*>(sample_rows_kernel<T, kLut, kGuided>),
+                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Shared<kLut, kGuided>));
 }
 
 template <typename T, bool kLut>
@@ -2134,6 +2165,24 @@ static cudaError_t launch_sample_t(
     cudaStream_t stream) {
   const cudaError_t attr = prepare_sample_kernel<T, kLut>();
   if (attr != cudaSuccess) return attr;
+  if (row_list != nullptr) {
+    // the pass over the rows that a fast kernel left undecided: resident early, waits for its
+    // predecessor before it reads the list
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(Shared<kLut>);
+    cfg.stream = stream;
+    cudaLaunchAttribute la[1];
+    programmatic_launch(&la[0]);
+    cfg.attrs = la;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sample_rows_kernel<T, kLut, false>, static_cast<const T*>(logits), rows, vocab,
+                              row_stride, inv_t, topp, topk, rng_states, out_ids, peers,
+                              static_cast<Entry*>(scratch), table, status, row_list, row_count,
+                              static_cast<int*>(nullptr), static_cast<int*>(nullptr), static_cast<int*>(nullptr),
+                              RowSettings{nullptr, nullptr, nullptr, 1.0f});
+  }
   sample_rows_kernel<T, kLut, false><<<blocks, kThreads, sizeof(Shared<kLut>), stream>>>(
       static_cast<const T*>(logits), rows, vocab, row_stride, inv_t, topp, topk, rng_states, out_ids,
       peers,
@@ -2331,14 +2380,16 @@ cudaError_t launch_topp_cluster(
     cudaStream_t stream) {
   const int csize = cluster_size_for(vocab);
   const int slice_len = ((vocab + csize * kCTerms - 1) / (csize * kCTerms)) * kCTerms;
-  cudaError_t e = cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)sizeof(ClusterShared));
+  static OncePerDevice once_a, once_b, once_np;
+  cudaError_t e = func_attr_once(once_a, reinterpret_cast<const void*>(topp_cluster_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ClusterShared));
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(topp_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)sizeof(FinishShared));
+  e = func_attr_once(once_b, reinterpret_cast<const void*>(topp_finish_kernel),
+                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FinishShared));
   if (e != cudaSuccess) return e;
   if (csize > 8) {
-    e = cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    e = func_attr_once(once_np, reinterpret_cast<const void*>(topp_cluster_kernel),
+                       cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return e;
   }
   const unsigned short* base = static_cast<const unsigned short*>(logits);
@@ -2359,10 +2410,19 @@ cudaError_t launch_topp_cluster(
     e = cudaLaunchKernelEx(&cfg, topp_cluster_kernel, base + row0 * row_stride, vocab, row_stride, slice_len,
                            inv_t, topp, table, static_cast<SliceScratch*>(scratch));
     if (e != cudaSuccess) return e;
-    topp_finish_kernel<<<(unsigned)n, kFThreads, sizeof(FinishShared), stream>>>(
-        static_cast<const SliceScratch*>(scratch), row0, rows, vocab, csize, topp, rng_states, out_ids, peers,
-        retry_rows, retry_count, row0 == 0 ? retry_count_next : nullptr);
-    e = cudaGetLastError();
+    // the finishing kernel may become resident while the cluster kernel runs (it waits for it)
+    cudaLaunchConfig_t fcfg = {};
+    fcfg.gridDim = dim3((unsigned)n, 1, 1);
+    fcfg.blockDim = dim3(kFThreads, 1, 1);
+    fcfg.dynamicSmemBytes = sizeof(FinishShared);
+    fcfg.stream = stream;
+    cudaLaunchAttribute fattr[1];
+    programmatic_launch(&fattr[0]);
+    fcfg.attrs = fattr;
+    fcfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&fcfg, topp_finish_kernel, static_cast<const SliceScratch*>(scratch), row0, rows, vocab,
+                           csize, topp, rng_states, out_ids, peers, retry_rows, retry_count,
+                           row0 == 0 ? retry_count_next : static_cast<int*>(nullptr));
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
