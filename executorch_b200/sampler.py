@@ -250,8 +250,9 @@ class Sampler:
 
     @property
     def status(self) -> int:
-        """Reads and clears the device status word (synchronises): 0, or 2 after an arrival
-        wait of ``sample_rows_exchange`` ran out."""
+        """Reads and clears the device status word (synchronises): 0, 2 after an arrival wait of
+        ``sample_rows_exchange`` ran out, 3 if the long-nucleus tail found its counts inconsistent
+        for some row (not expected)."""
         v = C.c_int32(0)
         _lib.check(_lib.load().etb200_sampler_get_status(self._h, C.byref(v)))
         return int(v.value)

@@ -87,3 +87,50 @@ def test_misaligned_strided_view(cuda_device, restatement):
         s.close()
         want = restatement.sample_rows(xh, 1.0, 0.9, seeds, dtype=dtype)
         assert np.array_equal(got, want), dtype
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_rows_with_their_own_settings_and_a_multiply(cuda_device, restatement, dtype):
+    """The extended entry point: every row its own temperature / top-p, a multiply processor folded
+    into the reads; long and short nuclei, greedy and multinomial rows mixed in one launch."""
+    rng = np.random.default_rng(34)
+    vocab, rows = 60_000, 40
+    kinds = [KINDS[r % len(KINDS)] for r in range(rows)]
+    x = np.stack([_bits(_rows(rng, k, vocab), dtype) for k in kinds])
+    temps = rng.choice([0.0, 0.7, 1.0, 1.5], size=rows).astype(np.float32)
+    topps = rng.choice([0.5, 0.9, 0.97, 1.0], size=rows).astype(np.float32)
+    seeds = rng.integers(1, 2**62, size=rows).astype(np.uint64)
+    scale = 0.5
+    # the multiply works in place on the stored type: the product is rounded to it
+    with np.errstate(invalid="ignore"):
+        xs = _bits(W.to_f32(x, dtype) * np.float32(scale), dtype)
+    want = np.array([restatement.sample_rows(xs[r:r + 1], float(temps[r]), float(topps[r]), seeds[r:r + 1],
+                                             dtype=dtype)[0] for r in range(rows)])
+    s = Sampler(vocab, 0.8, 0.9, 0, device=cuda_device)
+    try:
+        t = torch.from_numpy(np.ascontiguousarray(x).view(np.int16)).to(cuda_device)
+        t = t.view(torch.bfloat16 if dtype == "bf16" else torch.float16)
+        ids = s.sample_rows_ex(t, seeds_to_states(seeds, cuda_device),
+                               temperature=torch.from_numpy(temps).to(cuda_device),
+                               topp=torch.from_numpy(topps).to(cuda_device), scale=scale)
+        torch.cuda.synchronize()
+        got = ids.cpu().numpy()
+        assert np.array_equal(got, want), [(int(r), kinds[r], float(temps[r]), float(topps[r]))
+                                            for r in np.nonzero(got != want)[0][:8]]
+        assert s.status == 0
+    finally:
+        s.close()
+
+
+def test_more_long_rows_per_block_than_pending_records(cuda_device, restatement):
+    """2 400 flat rows: every block meets more long-nucleus rows than the eight it records before it
+    runs their tails, so the record list is flushed in the middle of the row loop."""
+    rng = np.random.default_rng(35)
+    vocab, rows = 40_001, 2_400
+    base = np.stack([_bits(_rows(rng, "flat", vocab), "bf16") for _ in range(16)])
+    x = np.tile(base, (rows // 16, 1))
+    x[::7] = _bits(_rows(rng, "peaked", vocab), "bf16")  # rows that keep the sorted path in between
+    seeds = rng.integers(0, 2**62, size=rows).astype(np.uint64)
+    want = restatement.sample_rows(x, 1.0, 0.9, seeds, dtype="bf16", threads=16)
+    got = gpu_sample(x, "bf16", 1.0, 0.9, seeds, cuda_device)
+    assert np.array_equal(got, want), np.nonzero(got != want)[0][:8]
