@@ -300,7 +300,14 @@ __device__ VcHit vc_walk(S& sm, const RowMath<T, S>& rm, float sum, float cutoff
               cj = c[j];
             }
           }
-          const int copies = class_hit_step(&st, pj, cj, thr, &found, &cum);
+          int copies = class_hit_step(&st, pj, cj, thr, &found, &cum);
+          // a long run may carry the sum through further binades: stay with it instead of
+          // paying a block round per binade
+          while (!found && copies < cj) {
+            const int rest = cj - copies;
+            if (seq_apply(st.n, rep_summary(pj, rest, st.kb)) < thr_limit(thr, st.kb)) break;
+            copies += class_hit_step(&st, pj, rest, thr, &found, &cum);
+          }
           vc.found = found ? 1 : 0;
           vc.kb = st.kb;
           vc.n = st.n;

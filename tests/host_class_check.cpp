@@ -94,7 +94,12 @@ int hcc_walk(const float* p, const int* count_in, int n_classes, float thr, int 
       s2.n = n_at;
       bool found;
       float c;
-      const int j = class_hit_step(&s2, p[hit_b], count[hit_b], thr, &found, &c);
+      int j = class_hit_step(&s2, p[hit_b], count[hit_b], thr, &found, &c);
+      while (!found && j < count[hit_b]) {  // the same run through further binades, as the kernel does
+        const int rest = count[hit_b] - j;
+        if (seq_apply(s2.n, rep_summary(p[hit_b], rest, s2.kb)) < thr_limit(thr, s2.kb)) break;
+        j += class_hit_step(&s2, p[hit_b], rest, thr, &found, &c);
+      }
       const long hit_pos = consumed + cnt_at + j - 1;
       if (found) {
         *cum = c;

@@ -134,3 +134,37 @@ def test_more_long_rows_per_block_than_pending_records(cuda_device, restatement)
     want = restatement.sample_rows(x, 1.0, 0.9, seeds, dtype="bf16", threads=16)
     got = gpu_sample(x, "bf16", 1.0, 0.9, seeds, cuda_device)
     assert np.array_equal(got, want), np.nonzero(got != want)[0][:8]
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_random_long_nucleus_campaign(cuda_device, restatement, dtype):
+    """1 200 random rows per dtype: random scale and shape of the logits (so that the nucleus is
+    anything from a few thousand tokens to the whole row), random vocabulary size, temperature and
+    top-p; a batch mixes rows that take the value-class tail with rows that keep the sorted path."""
+    rng = np.random.default_rng(36 if dtype == "fp16" else 37)
+    for batch in range(6):
+        vocab = int(rng.integers(33_000, 90_000))
+        rows = 200
+        v = np.empty((rows, vocab), dtype=np.float32)
+        for r in range(rows):
+            kind = r % 5
+            if kind == 0:      # nearly uniform
+                v[r] = rng.uniform(0.005, 0.3) * rng.standard_normal(vocab)
+            elif kind == 1:    # unit normal with a few hot tokens
+                v[r] = rng.standard_normal(vocab)
+                v[r, rng.integers(0, vocab, 3)] = rng.uniform(4, 14)
+            elif kind == 2:    # heavy duplicates: logits on a coarse grid
+                step = rng.choice([0.125, 0.25, 0.5])
+                v[r] = np.round(rng.standard_normal(vocab) / step) * step
+            elif kind == 3:    # Zipf-shaped: usually a short nucleus, the sorted path
+                v[r] = -1.1 * np.log(1.0 + rng.permutation(vocab)) + 0.5 * rng.standard_normal(vocab)
+            else:              # offset far from zero, both signs in different rows
+                v[r] = rng.choice([-30.0, 30.0]) + rng.uniform(0.02, 1.5) * rng.standard_normal(vocab)
+        x = _bits(v, dtype)
+        seeds = rng.integers(0, 2**62, size=rows).astype(np.uint64)
+        t = float(rng.choice([0.6, 1.0, 1.7, 3.0]))
+        p = float(rng.choice([0.3, 0.8, 0.9, 0.97, 0.999]))
+        want = restatement.sample_rows(x, t, p, seeds, dtype=dtype, threads=16)
+        got = gpu_sample(x, dtype, t, p, seeds, cuda_device)
+        bad = np.nonzero(got != want)[0]
+        assert len(bad) == 0, (dtype, batch, vocab, t, p, [(int(r), int(r) % 5) for r in bad[:8]])
