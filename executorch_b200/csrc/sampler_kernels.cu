@@ -2363,17 +2363,17 @@ bool topp_cluster_supported(int dtype, const void* logits, int64_t rows, int voc
   return true;
 }
 
-// Blocks per row. A batch uses as few as hold the row (more rows in flight); a single row is
-// latency and nothing else, so it is spread over twice as many SMs where the hardware allows.
-static int cluster_size_for(int vocab, int64_t rows) {
+// Blocks per row: as few as hold the row. (Twice as many for a single row was measured and is no
+// quicker: the cluster kernel's chain of barriers does not get shorter, and the finishing kernel
+// gets twice the slices to join.)
+static int cluster_size_for(int vocab) {
   int csize = 1;
   while (csize * kCSliceMax < vocab) csize *= 2;
-  if (rows == 1 && csize * 2 <= kCMaxCluster && vocab >= 2 * csize * kCTerms * 32) csize *= 2;
   return csize;
 }
 
 size_t topp_cluster_scratch_bytes(int vocab, int64_t batch_rows) {
-  return (size_t)batch_rows * (size_t)cluster_size_for(vocab, batch_rows) * sizeof(SliceScratch);
+  return (size_t)batch_rows * (size_t)cluster_size_for(vocab) * sizeof(SliceScratch);
 }
 
 cudaError_t launch_topp_cluster(
@@ -2381,7 +2381,7 @@ cudaError_t launch_topp_cluster(
     unsigned long long* rng_states, int64_t* out_ids, const PeerOut& peers, const ExpTable& table,
     void* scratch, int64_t batch_rows, int* retry_rows, int* retry_count, int* retry_count_next,
     cudaStream_t stream) {
-  const int csize = cluster_size_for(vocab, rows);
+  const int csize = cluster_size_for(vocab);
   const int slice_len = ((vocab + csize * kCTerms - 1) / (csize * kCTerms)) * kCTerms;
   static OncePerDevice once_a, once_b, once_np;
   cudaError_t e = func_attr_once(once_a, reinterpret_cast<const void*>(topp_cluster_kernel),
