@@ -7,8 +7,9 @@
 // classes in descending key order, every class a run of `count` equal floats. Nothing is
 // listed, compacted or sorted here:
 //
-//   1. count the row's patterns into a window of kVcBins classes below the row maximum
-//      (shared-memory histogram; one read of the row per window),
+//   1. count the row's patterns into a window of classes below the row maximum (shared-memory
+//      histogram, 2 * kVcBins 16-bit counters, or kVcBins 32-bit ones for a row in which a class
+//      holds 65 536 or more logits; one read of the row per window),
 //   2. walk the classes, replaying `cumulative_prob += p` (sampler.cpp:151) over whole runs in
 //      closed form (class_math.cuh) until the sum exceeds top-p; then again until it exceeds
 //      r = coin * cumulative_prob (sampler.cpp:162-170). The result is a POSITION of the
@@ -72,10 +73,14 @@ __device__ __forceinline__ void vc_load8(const RowMath<T, S>& rm, int i0, uint32
   }
 }
 
-// Counts the row's patterns with keys in (win_hi - kVcBins, win_hi] into the window (vc_hist), slot
-// win_hi - key: slot 0 is the window's largest value.
+// Counts the row's patterns with keys in (win_hi - span, win_hi] into the window (vc_hist), slot
+// win_hi - key: slot 0 is the window's largest value. With `pack16` the counters are 16 bits
+// wide (two per word, span 2 * kVcBins): twice the classes per read of the row. A class of 65 536
+// or more equal logits overflows such a counter; then the window's counters no longer add up to
+// the number of logits counted, which is checked here, and the caller starts over with 32-bit
+// counters. Returns false in that case (block-uniform).
 template <typename T, typename S>
-__device__ void vc_histogram(S& sm, const RowMath<T, S>& rm, int win_hi) {
+__device__ bool vc_histogram(S& sm, const RowMath<T, S>& rm, int win_hi, bool pack16) {
   const int tid = threadIdx.x;
   unsigned* hist = vc_hist(sm);
   __syncthreads();
@@ -83,7 +88,9 @@ __device__ void vc_histogram(S& sm, const RowMath<T, S>& rm, int win_hi) {
     reinterpret_cast<uint4*>(hist)[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   __syncthreads();
+  const uint32_t span = pack16 ? 2u * kVcBins : (uint32_t)kVcBins;
   const int nvec = (rm.vocab + 7) / 8;
+  int added = 0;
   for (int q0 = tid; q0 < nvec; q0 += 4 * kThreads) {
     uint32_t w[4][4];
 #pragma unroll
@@ -101,15 +108,38 @@ __device__ void vc_histogram(S& sm, const RowMath<T, S>& rm, int win_hi) {
       for (int j = 0; j < 4; ++j) {
         const uint32_t d0 = (uint32_t)win_hi - key_of_pattern16(w[k][j] & 0xFFFFu);
         const uint32_t d1 = (uint32_t)win_hi - key_of_pattern16(w[k][j] >> 16);
-        if (d0 < (uint32_t)kVcBins) atomicAdd(&hist[d0], 1u);
-        if (d1 < (uint32_t)kVcBins) atomicAdd(&hist[d1], 1u);
+        if (pack16) {
+          if (d0 < span) {
+            atomicAdd(&hist[d0 >> 1], 1u << ((d0 & 1u) * 16u));
+            ++added;
+          }
+          if (d1 < span) {
+            atomicAdd(&hist[d1 >> 1], 1u << ((d1 & 1u) * 16u));
+            ++added;
+          }
+        } else {
+          if (d0 < span) atomicAdd(&hist[d0], 1u);
+          if (d1 < span) atomicAdd(&hist[d1], 1u);
+        }
       }
     }
   }
   __syncthreads();
+  if (!pack16) return true;
+  // every thread: the counters of its share of the window against what it added
+  int diff = added;
+  for (int i = tid; i < kVcBins / 4; i += kThreads) {
+    const uint4 q = reinterpret_cast<const uint4*>(hist)[i];
+    diff -= (int)((q.x & 0xFFFFu) + (q.x >> 16) + (q.y & 0xFFFFu) + (q.y >> 16) + (q.z & 0xFFFFu) + (q.z >> 16) +
+                  (q.w & 0xFFFFu) + (q.w >> 16));
+  }
+  int total;
+  block_excl_count(sm, diff, &total);
+  return total == 0;
 }
 
 struct VcHit {
+  bool overflow;  // a 16-bit class counter overflowed: nothing is decided, start over with 32-bit counters
   bool found;  // the running sum exceeded the threshold
   int pos;     // found: position (0-based) of the copy at which it did; else the number of candidates
   float p;     // found: the probability at that position
@@ -122,9 +152,10 @@ struct VcHit {
 // beyond its threshold. Block-uniform result.
 template <typename T, typename S>
 __device__ VcHit vc_walk(S& sm, const RowMath<T, S>& rm, float sum, float cutoff, float thr, int key_max,
-                         int key_min, bool first_walk) {
+                         int key_min, bool first_walk, bool pack16) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   VcControl& vc = sm.vcc;
+  const int span = pack16 ? 2 * kVcBins : kVcBins;  // classes per window
   int win_hi = key_max, kb = 1, n = 0, pos = 0;
   if (!first_walk) {
     const int nck = vc.n_ck;
@@ -138,6 +169,7 @@ __device__ VcHit vc_walk(S& sm, const RowMath<T, S>& rm, float sum, float cutoff
     }
   }
   VcHit out;
+  out.overflow = false;
   for (;;) {
     if (first_walk && tid == 0 && vc.n_ck < kVcCheckpoints) {
       const int i = vc.n_ck;
@@ -151,14 +183,35 @@ __device__ VcHit vc_walk(S& sm, const RowMath<T, S>& rm, float sum, float cutoff
     if (vc_prob(rm, sm, (uint32_t)win_hi, sum) < cutoff) break;     // nothing below is a candidate
     if (vc.loaded_hi != win_hi) {
       ETB_CLOCK_BEGIN();
-      vc_histogram(sm, rm, win_hi);
+      const bool counted = vc_histogram(sm, rm, win_hi, pack16);
       ETB_CLOCK_ADD(11);
-      if (tid == 0) vc.loaded_hi = win_hi;
+      if (tid == 0) vc.loaded_hi = counted ? win_hi : -1;
+      if (!counted) {
+        out.overflow = true;
+        out.found = false;
+        out.pos = 0;
+        out.p = 0.0f;
+        out.cum = 0.0f;
+        __syncthreads();
+        return out;
+      }
     }
-    for (int t0 = 0; t0 < kVcBins; t0 += kVcTile) {
+    for (int t0 = 0; t0 < span; t0 += kVcTile) {
       const int b0 = t0 + tid * kVcPer;
-      const uint4 cv = *reinterpret_cast<const uint4*>(&vc_hist(sm)[b0]);
-      int c[kVcPer] = {(int)cv.x, (int)cv.y, (int)cv.z, (int)cv.w};
+      int c[kVcPer];
+      if (pack16) {
+        const uint2 cv = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(vc_hist(sm)) + b0);
+        c[0] = (int)(cv.x & 0xFFFFu);
+        c[1] = (int)(cv.x >> 16);
+        c[2] = (int)(cv.y & 0xFFFFu);
+        c[3] = (int)(cv.y >> 16);
+      } else {
+        const uint4 cv = *reinterpret_cast<const uint4*>(&vc_hist(sm)[b0]);
+        c[0] = (int)cv.x;
+        c[1] = (int)cv.y;
+        c[2] = (int)cv.z;
+        c[3] = (int)cv.w;
+      }
       float p[kVcPer];
       bool below = false;
       int low_key = 0x7fffffff;
@@ -343,7 +396,7 @@ __device__ VcHit vc_walk(S& sm, const RowMath<T, S>& rm, float sum, float cutoff
       __syncthreads();
       if (vc.ended) goto done;
     }
-    win_hi -= kVcBins;
+    win_hi -= span;
     if (win_hi < key_min) break;
   }
 done:
@@ -475,33 +528,49 @@ __device__ __forceinline__ int value_class_tail(S& sm, const RowMath<T, S>& rm, 
   }
   const int key_max = (int)key_of_pattern16(max_pat);
   const int key_min = (int)key_of_pattern16(std::is_same<T, __nv_bfloat16>::value ? 0xFF80u : 0xFC00u);
-  __syncthreads();
-  if (tid == 0) {
-    vc.hit_tid = 0x7fffffff;
-    vc.ended = 0;
-    vc.last_key = 0xFFFFFFFFu;
-    vc.loaded_hi = -1;
-    vc.n_ck = 0;
-  }
-  __syncthreads();
-  ETB_STAMP(7);
-  const VcHit first = vc_walk(sm, rm, sum, cutoff, topp, key_max, key_min, true);
-  ETB_STAMP(8);
-  if (first.pos <= 0 && !first.found) return -1;  // no candidate at all
-  // last_idx and the sum there (sampler.cpp:147-158); without a hit every candidate is kept
-  int pos = first.found ? first.pos : first.pos - 1;
-  float pstar = first.p;
-  const float r = __fmul_rn(coin, first.cum);  // sampler.cpp:162
-  if (r < first.cum) {
-    // the first position whose running sum exceeds r lies at or before last_idx
+  int pos = 0;
+  float pstar = 0.0f;
+  // A flat row (softmax sum of the order of the vocabulary size: most terms are close to the
+  // largest) has candidates over more classes than one 32-bit window holds: 16-bit class counters
+  // first for it (twice the classes per read of the row), and if one of them overflows (65 536 or
+  // more equal logits) everything again with 32-bit counters. Other rows usually end inside the
+  // first 32-bit window, where the packed form only costs (its check, and neighbouring classes
+  // sharing a word).
+  const bool flat = sum > 0.125f * (float)rm.vocab;
+#pragma unroll 1
+  for (int attempt = flat ? 0 : 1; attempt < 2; ++attempt) {
+    const bool pack16 = attempt == 0;
     __syncthreads();
-    if (tid == 0) vc.ended = 0;
-    __syncthreads();
-    const VcHit second = vc_walk(sm, rm, sum, cutoff, r, key_max, key_min, false);
-    if (second.found && second.pos <= pos) {
-      pos = second.pos;
-      pstar = second.p;
+    if (tid == 0) {
+      vc.hit_tid = 0x7fffffff;
+      vc.ended = 0;
+      vc.last_key = 0xFFFFFFFFu;
+      vc.loaded_hi = -1;
+      vc.n_ck = 0;
     }
+    __syncthreads();
+    ETB_STAMP(7);
+    const VcHit first = vc_walk(sm, rm, sum, cutoff, topp, key_max, key_min, true, pack16);
+    ETB_STAMP(8);
+    if (first.overflow) continue;
+    if (first.pos <= 0 && !first.found) return -1;  // no candidate at all
+    // last_idx and the sum there (sampler.cpp:147-158); without a hit every candidate is kept
+    pos = first.found ? first.pos : first.pos - 1;
+    pstar = first.p;
+    const float r = __fmul_rn(coin, first.cum);  // sampler.cpp:162
+    if (r < first.cum) {
+      // the first position whose running sum exceeds r lies at or before last_idx
+      __syncthreads();
+      if (tid == 0) vc.ended = 0;
+      __syncthreads();
+      const VcHit second = vc_walk(sm, rm, sum, cutoff, r, key_max, key_min, false, pack16);
+      if (second.overflow) continue;
+      if (second.found && second.pos <= pos) {
+        pos = second.pos;
+        pstar = second.p;
+      }
+    }
+    break;
   }
   ETB_STAMP(9);
   const int token = vc_select(sm, rm, sum, key_max, key_min, pos, pstar);
