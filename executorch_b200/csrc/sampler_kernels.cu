@@ -105,7 +105,7 @@ static_assert(kGEventCap <= kThreads, "one thread per event resolves the pending
 
 // Shared state of the value-class tail (value_class_tail.cuh): a window of class counts, later
 // reused for per-(tile, thread) member counts, and the block's walk record.
-constexpr int kVcBins = 16384;                 // value classes per window
+constexpr int kVcBins = 16384;                 // 32-bit class counters of a window (or twice as many 16-bit ones)
 constexpr int kVcPer = 4;                      // classes per thread in one round of the walk
 constexpr int kVcTile = kThreads * kVcPer;
 constexpr int kVcSelTile = kThreads * 32;      // logits per tile of the final lookup
@@ -115,7 +115,7 @@ constexpr int kVcListProbe = 2048;             // from this many on, the count s
 constexpr int kVcMinNucleus = 4096;            // ... and so does one whose list is short of this many, at least
 constexpr int kVcPendCap = 8;                  // deferred tails a block collects before it runs them
 constexpr int kVcCheckpoints = 6;              // window starts of one row (65536 keys / kVcBins, and one)
-static_assert(kVcPer == 4, "a thread reads its four class counts as one 128-bit word");
+static_assert(kVcPer == 4, "a thread reads its four class counts as one 128-bit (or 64-bit) word");
 
 struct VcHist {
   alignas(16) unsigned hist[kVcBins];

@@ -8,8 +8,9 @@
 // listed, compacted or sorted here:
 //
 //   1. count the row's patterns into a window of classes below the row maximum (shared-memory
-//      histogram, 2 * kVcBins 16-bit counters, or kVcBins 32-bit ones for a row in which a class
-//      holds 65 536 or more logits; one read of the row per window),
+//      histogram of kVcBins 32-bit counters; for a flat row, whose candidates span more classes,
+//      2 * kVcBins 16-bit counters unless a class holds 65 536 or more logits; one read of the
+//      row per window),
 //   2. walk the classes, replaying `cumulative_prob += p` (sampler.cpp:151) over whole runs in
 //      closed form (class_math.cuh) until the sum exceeds top-p; then again until it exceeds
 //      r = coin * cumulative_prob (sampler.cpp:162-170). The result is a POSITION of the
