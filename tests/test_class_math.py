@@ -119,3 +119,19 @@ def test_key_order(hcc):
     ok = np.isfinite(vals)
     order = np.argsort(keys[ok], kind="stable")
     assert (np.diff(vals[ok][order]) >= 0).all()
+
+
+def test_runs_as_long_as_the_largest_vocabulary(hcc):
+    """A few classes of up to 524 288 copies (the tail's vocabulary limit): products of count and
+    increment beyond 32 bits, sums that cross many binades inside one run, thresholds of zero and
+    beyond the total."""
+    rng = np.random.default_rng(13)
+    for trial in range(40):
+        n = int(rng.integers(1, 6))
+        p = np.sort(rng.choice([1.9e-6, 3e-7, 2.0 ** -20, 1.5 * 2.0 ** -19, 7.3e-3, 1e-38, 3e-41], n))[::-1]
+        cnt = rng.integers(1, 524_289, n)
+        p32, c32 = p.astype(np.float32), cnt.astype(np.int32)
+        total = float(np.sum(p32.astype(np.float64) * c32))
+        for thr in (0.0, total * 0.37, total * 0.999, total * 2.0 + 1e-30):
+            a, b, _ = _both(hcc, p32, c32, np.float32(thr), threads=int(rng.integers(1, 8)), per_thread=4)
+            assert a == b, (trial, p32, c32, thr, a, b)
